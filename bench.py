@@ -1,0 +1,366 @@
+"""Benchmark of the quantized-linear hot path on B200.
+
+Workload (N = 1): the W8A8 prefill sweep — M = 8192 tokens through the four
+Qwen3-0.6B projections (qkv 1024->4096, o 2048->1024, gate_up 1024->6144,
+down 3072->1024).  One step = for each projection: per-token activation
+quantisation (bf16 -> int8 + scale) followed by the int8 GEMM with the fused scale
+epilogue (bf16 out).  Inputs are seeded synthetic tensors (N(0,1) activations with
+1 % outlier channels x20, N(0,0.02) weights quantised per channel).
+
+With --gpus N > 1 (launched by torchrun, one rank per GPU) the same 8192 tokens run
+tensor-parallel: qkv / gate_up split their output channels, o / down split their input
+features and are followed by an NCCL all-reduce of the bf16 result ("strong" scaling).
+
+Prints ONE JSON line (rank 0).  ``value`` is device-timed with inputs resident in HBM;
+``e2e`` goes through the layer API with host buffers (H2D of activations, D2H of
+outputs inside the timed region); ``roofline`` is for the GEMM kernel, from CUDA-event
+durations of its launches inside the timed region; ``cpu_baseline`` times the CPU
+oracle's dequantize-then-matmul path on the host cores.
+
+``--impl reference`` times the reference's CPU algorithm (the oracle port of its
+dequantize-then-matmul path) on the host cores for the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+TOKENS = 8192
+# name, K (in features), N (out features), tensor-parallel split: "col" splits N, "row" splits K
+PROJECTIONS = [("qkv", 1024, 4096, "col"), ("o", 2048, 1024, "row"),
+               ("gate_up", 1024, 6144, "col"), ("down", 3072, 1024, "row")]
+METRIC = "quant GEMM TOPS (W8A8 prefill sweep: act-quant + int8 GEMM, M=8192, Qwen3-0.6B qkv/o/gate_up/down)"
+
+
+def total_ops(tokens: int = TOKENS) -> float:
+    return float(sum(2 * tokens * k * n for _, k, n, _ in PROJECTIONS))
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"],
+                "bf16_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_sweep_seconds(tokens: int, repeats: int):
+    """Best-of-``repeats`` wall time of the CPU oracle's W8A8 path (per-token quantise, then
+    dequantise both operands and matmul) over the four projections for ``tokens`` tokens."""
+    from oracle import quant_linear_oracle as O
+    problems = []
+    for i, (_, K, N, _) in enumerate(PROJECTIONS):
+        q, s = O.make_weight(N, K, seed=i)
+        x = O.make_activation(tokens, K, seed=i)
+        problems.append((x, q, s))
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for x, q, s in problems:
+            xf = x.float()
+            a_s = (xf.abs().amax(dim=1) / 127.0).clamp_min(1e-8)
+            xq = torch.round(xf / a_s[:, None]).clamp(-127, 127).to(torch.int8)
+            O.w8a8_dequant_matmul(xq, a_s, q, s, None, torch.bfloat16)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def cpu_baseline(budget_s: float = 20.0):
+    threads = torch.get_num_threads()
+    probe_tokens = 256
+    t_probe = cpu_sweep_seconds(probe_tokens, 1)
+    per_token = t_probe / probe_tokens
+    tokens = int(min(TOKENS, max(256, (budget_s / 3.0) / per_token)))
+    tokens = max(256, tokens // 256 * 256)
+    t = cpu_sweep_seconds(tokens, 3)
+    return {"value": total_ops(tokens) / t / 1e12, "unit": "TOPS", "cores": threads, "kind": "port",
+            "sample": f"{tokens} of {TOKENS} tokens through all four projections, best of 3 passes, "
+                      f"torch CPU bf16 dequantize-then-matmul (oracle port), {threads} threads of "
+                      f"{os.cpu_count()} logical CPUs",
+            "seconds": t}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = torch.get_num_threads()
+    t_probe = cpu_sweep_seconds(256, 1)
+    tokens = int(min(TOKENS, max(256, 1.5 / (t_probe / 256))))  # about 1.5 s per step at most
+    tokens = max(256, tokens // 256 * 256)
+    for _ in range(max(0, min(args.warmup, 3))):
+        cpu_sweep_seconds(tokens, 1)
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_sweep_seconds(tokens, 1)
+    dt = (time.perf_counter() - t0) / steps
+    value = total_ops(tokens) / dt / 1e12
+    sample = (f"{tokens} of {TOKENS} tokens per step, {steps} timed steps, torch CPU bf16 "
+              f"dequantize-then-matmul (oracle port of the reference's Python path)")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": args.gpus,
+        "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "configs[1] W8A8 prefill sweep, CPU sample", "tokens": tokens,
+                   "parallelism": "cpu"},
+        "cpu_baseline": {"value": value, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# --------------------------------------------------------------------------- GPU arm
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.06)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [c.strip() for c in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def run_gpu_arm(args):
+    import torch.distributed as dist
+
+    import tiny_vllm_b200  # noqa: F401
+    from oracle import quant_linear_oracle as O
+    from tiny_vllm_b200 import _lib
+    from tiny_vllm_b200.layers import linear as LL
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback of the product path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tp = world
+    L = _lib.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    # ---- layers (public API) and raw buffers (kernel-only loop), per-rank shapes
+    prev_dtype = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    layers, work = [], []
+    with torch.device(dev):
+        for i, (name, K, N, split) in enumerate(PROJECTIONS):
+            q_full, s_full = O.make_weight(N, K, seed=i)
+            x_full = O.make_activation(TOKENS, K, seed=i)
+            if name == "qkv":
+                layer = LL.QKVParallelLinear(K, 128, 16, 8, quantization="w8a8")
+            elif name == "gate_up":
+                layer = LL.MergedColumnParallelLinear(K, [N // 2, N // 2], quantization="w8a8")
+            else:
+                layer = LL.RowParallelLinear(K, N, quantization="w8a8")
+            layer.qweight.weight_loader(layer.qweight, q_full)
+            layer.w_scales.weight_loader(layer.w_scales, s_full)
+            x_local = x_full if split == "col" else x_full.chunk(tp, dim=1)[rank].contiguous()
+            layers.append(layer)
+            n_loc, k_loc = layer.qweight.shape
+            work.append({
+                "name": name, "split": split, "K": k_loc, "N": n_loc,
+                "x_host": x_local.pin_memory(), "x": x_local.to(dev),
+                "xq": torch.empty(TOKENS, k_loc, dtype=torch.int8, device=dev),
+                "a_s": torch.empty(TOKENS, dtype=torch.float32, device=dev),
+                "y": torch.empty(TOKENS, n_loc, dtype=torch.bfloat16, device=dev),
+                "y_host": torch.empty(TOKENS, n_loc, dtype=torch.bfloat16).pin_memory(),
+                "layer": layer, "ops": 2.0 * TOKENS * k_loc * n_loc,
+            })
+    torch.set_default_dtype(prev_dtype)
+    ws_bytes = max([L.b200q_workspace_bytes(_lib.OP_W8A8, TOKENS, w["N"], w["K"]) for w in work] + [16])
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
+
+    def kernel_step(events=None):
+        for w in work:
+            rc = L.b200q_act_quant_i8(w["x"].data_ptr(), w["K"], _lib.DTYPE_BF16, w["xq"].data_ptr(),
+                                      w["a_s"].data_ptr(), TOKENS, w["K"], stream)
+            _lib.check(rc, "b200q_act_quant_i8")
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+            rc = L.b200q_w8a8_gemm(w["xq"].data_ptr(), w["a_s"].data_ptr(), w["layer"].qweight.data_ptr(),
+                                   w["layer"].w_scales.data_ptr(), None, w["y"].data_ptr(), TOKENS,
+                                   w["N"], w["K"], _lib.DTYPE_BF16, ws.data_ptr(), ws.numel(), stream)
+            _lib.check(rc, "b200q_w8a8_gemm")
+            if events is not None:
+                e1 = torch.cuda.Event(enable_timing=True)
+                e1.record()
+                events.append((w["name"], e0, e1))
+            if w["split"] == "row" and tp > 1:
+                dist.all_reduce(w["y"])
+
+    def e2e_step():
+        for w in work:
+            x = w["x_host"].to(dev, non_blocking=True)
+            y = w["layer"](x)                       # act-quant + GEMM (+ all-reduce) via the layer API
+            w["y_host"].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if tp > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- warm-up
+    for _ in range(max(3, args.warmup)):
+        kernel_step()
+    sync_all()
+    if L.b200q_device_status() != 0:
+        raise SystemExit("device status word set during warm-up: a bounded wait gave up")
+
+    # ---- timed region (device time, inputs resident in HBM)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = L.b200q_launch_count()
+    events = []
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    t_start.record()
+    for _ in range(args.steps):
+        kernel_step(events)
+    t_end.record()
+    sync_all()
+    elapsed_ms = t_start.elapsed_time(t_end)
+    launches = L.b200q_launch_count() - launches0
+    clocks = sampler.stop() if sampler is not None else None
+    if tp > 1:
+        t = torch.tensor([elapsed_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    full_ops = total_ops()
+    value = full_ops / (ms_per_step * 1e-3) / 1e12
+
+    # per-kernel durations of the GEMM launches inside the timed region
+    per_shape = {}
+    gemm_ms_total, gemm_ops_total = 0.0, 0.0
+    for name, e0, e1 in events:
+        per_shape.setdefault(name, []).append(e0.elapsed_time(e1))
+    ops_of = {w["name"]: w["ops"] for w in work}
+    bytes_of = {w["name"]: TOKENS * w["K"] + w["N"] * w["K"] + 4 * TOKENS + 4 * w["N"] + 2 * TOKENS * w["N"]
+                for w in work}
+    detail = {}
+    for name, ms in per_shape.items():
+        avg = sum(ms) / len(ms)
+        gemm_ms_total += sum(ms)
+        gemm_ops_total += ops_of[name] * len(ms)
+        detail[name] = {"gemm_us": avg * 1e3, "gemm_tops": ops_of[name] / (avg * 1e-3) / 1e12,
+                        "gemm_algorithmic_gbs": bytes_of[name] / (avg * 1e-3) / 1e9}
+    peaks = load_peaks()
+    int8_peak = 2.0 * peaks["bf16_sustained"]
+    achieved = gemm_ops_total / (gemm_ms_total * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
+                "frac": achieved / int8_peak, "traffic": None,
+                "kernel": "w8a8_umma_kernel (tcgen05 kind::i8)",
+                "peak_note": f"2 x {peaks['source']} sustained bf16 dense TFLOP/s ({peaks['bf16_sustained']}); "
+                             "int8 is the double-rate kind; nominal 4500"}
+
+    # ---- end-to-end through the layer API with host buffers
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    sync_all()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    if tp > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    h2d = sum(w["x_host"].numel() * 2 for w in work)
+    d2h = sum(w["y_host"].numel() * 2 for w in work)
+    e2e = {"value": full_ops / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps}
+
+    status = L.b200q_device_status()
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "configs[1]: W8A8 prefill GEMM sweep, M=8192, Qwen3-0.6B projections "
+                                   "(qkv 1024->4096, o 2048->1024, gate_up 1024->6144, down 3072->1024)",
+                       "tokens": TOKENS, "parallelism": f"tp{world}",
+                       "l2": "no flush: one step touches about 450 MB (activations, int8 copies, outputs), "
+                             "more than the 126 MB L2"},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "device_status": status, "detail": detail,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line))
+    if tp > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

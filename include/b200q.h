@@ -1,0 +1,166 @@
+/*
+ * b200q — C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * This header is the drop-in boundary for the quantized linear path of
+ * tiny-vLLM (a nano-vllm fork).  Each entry point names the reference interface
+ * it stands in for (paths are relative to the reference project root).
+ *
+ * Conventions shared by every compute entry point
+ *   - Plain pointers and sizes only; every pointer is DEVICE memory owned by the
+ *     caller.  The library allocates nothing per call and keeps only cached TMA
+ *     descriptors and kernel attributes.
+ *   - `stream` is a cudaStream_t passed as void*.  Work is always enqueued on
+ *     that stream (the reference launches on the legacy default stream instead:
+ *     nanovllm/quantization/csrc/w8a8_gemm.cu:438, int8_weight_only_gemm.cu:558),
+ *     so calls can be recorded by a CUDA-graph capture of that stream.
+ *   - No call synchronises the device and no call falls back to another
+ *     implementation: a non-zero return code means nothing was launched.
+ *   - Matrices are row-major and dense: x[M,K], qweight[N,K], y[M,N].
+ *   - K must be a multiple of 16 (the row pitch of an int8 [rows,K] matrix must
+ *     be 16-byte aligned for TMA); all base pointers must be 16-byte aligned.
+ *   - Return value: B200Q_OK (0) or one of the B200Q_ERR_* codes below;
+ *     b200q_strerror() gives the text.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200Q_VERSION 1
+
+/* ---- error codes ------------------------------------------------------- */
+enum {
+  B200Q_OK = 0,
+  B200Q_ERR_NULL_POINTER = 1,      /* a required pointer is NULL */
+  B200Q_ERR_BAD_SHAPE = 2,         /* M, N or K is <= 0 or overflows int32 indexing */
+  B200Q_ERR_UNSUPPORTED_SHAPE = 3, /* K % 16 != 0, or a stride rule is violated */
+  B200Q_ERR_MISALIGNED = 4,        /* a pointer is not 16-byte aligned */
+  B200Q_ERR_WORKSPACE = 5,         /* workspace is NULL or smaller than b200q_workspace_bytes() */
+  B200Q_ERR_UNSUPPORTED_ARCH = 6,  /* current device is not compute capability 10.x */
+  B200Q_ERR_LAUNCH = 7,            /* a CUDA runtime/driver call failed (see b200q_last_cuda_error) */
+  B200Q_ERR_BAD_ARGUMENT = 8,      /* unknown op / dtype / path id */
+  B200Q_ERR_DEVICE_TIMEOUT = 9     /* a bounded device-side wait gave up (b200q_device_status) */
+};
+
+/* ---- element types of the floating-point side -------------------------- */
+enum {
+  B200Q_DTYPE_F16 = 0,
+  B200Q_DTYPE_BF16 = 1
+};
+
+/* ---- operations (for workspace / path queries) ------------------------- */
+enum {
+  B200Q_OP_ACT_QUANT = 0,
+  B200Q_OP_W8A8 = 1,
+  B200Q_OP_W8A16 = 2
+};
+
+/* ---- kernel families (b200q_select_path ids / b200q_debug_force_path) --- */
+enum {
+  B200Q_PATH_AUTO = 0,
+  B200Q_PATH_SIMT_STREAM = 1, /* weight-streaming SIMT kernel, tiny M                    */
+  B200Q_PATH_UMMA = 2,        /* tcgen05 kernel, tokens on the 128-row side (prefill)     */
+  B200Q_PATH_UMMA_SWAP = 3    /* tcgen05 kernel, channels on the 128-row side + split-K   */
+};
+
+/*
+ * Per-token dynamic int8 quantisation of activations:
+ *   a_scales[m] = max(max_k |x[m,k]| / 127, 1e-8)            (fp32, IEEE division)
+ *   xq[m,k]     = clamp(round_half_even(x[m,k] / a_scales[m]), -127, 127)
+ * x is [M,K] with row pitch ldx elements (ldx >= K, ldx % 8 == 0), dtype per
+ * x_dtype; xq is dense int8 [M,K]; a_scales is fp32 [M].
+ * Replaces nanovllm/quantization/utils.py:28-32 (quantize_int8_per_row_dynamic),
+ * called from nanovllm/quantization/w8a8.py:21-23; results are bit-identical to it.
+ */
+int b200q_act_quant_i8(const void* x, int64_t ldx, int x_dtype, int8_t* xq, float* a_scales,
+                       int M, int K, void* stream);
+
+/*
+ * W8A8 linear: acc[m,n] = sum_k xq[m,k] * qweight[n,k] (exact int32), then
+ *   y[m,n] = out_dtype( (float(acc) * a_scales[m]) * w_scales[n] + bias[n] )
+ * bias may be NULL; when given it has dtype out_dtype and length N.
+ * Replaces the pybind entry `forward(x_q, a_scales, qweight, w_scales, bias,
+ * use_bfloat16)` of nanovllm/quantization/csrc/w8a8_gemm.cpp:16-54 and its
+ * launcher w8a8_gemm.cu:426-507 (epilogue arithmetic: w8a8_gemm.cu:387-390).
+ * workspace: b200q_workspace_bytes(B200Q_OP_W8A8, M, N, K) bytes (may be 0 -> NULL ok).
+ */
+int b200q_w8a8_gemm(const int8_t* xq, const float* a_scales, const int8_t* qweight,
+                    const float* w_scales, const void* bias, void* y, int M, int N, int K,
+                    int out_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Same contraction as b200q_w8a8_gemm but writes the raw int32 accumulators
+ * acc[M,N] and applies no epilogue.  The reference keeps these internal
+ * (nanovllm/quantization/csrc/w8a8_gemm.cu:336,377-390; integer MAC loop at
+ * w8a8_gemm.cu:165-183); this entry exists so that they can be compared bit for
+ * bit with a CPU integer matmul.
+ */
+int b200q_w8a8_gemm_i32(const int8_t* xq, const int8_t* qweight, int32_t* acc, int M, int N,
+                        int K, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * W8A16 linear: y[m,n] = x_dtype( scales[n] * sum_k x[m,k] * float(qweight[n,k]) + bias[n] ),
+ * fp32 accumulation, x and y and bias share x_dtype (fp16 or bf16).
+ * Replaces the pybind entry `forward(x2d, qweight, scales, bias)` of
+ * nanovllm/quantization/csrc/int8_weight_only_gemm.cpp:14-43 and its launcher
+ * int8_weight_only_gemm.cu:549-618.
+ */
+int b200q_w8a16_gemm(const void* x, const int8_t* qweight, const float* scales, const void* bias,
+                     void* y, int M, int N, int K, int x_dtype, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
+/*
+ * Scratch bytes the given op needs for the given problem (0 when none).  The
+ * first use of a workspace must find it zero-filled; every successful call
+ * leaves it zero-filled where that matters, so one zeroed buffer of the maximum
+ * size can be shared by all calls that are ordered on one stream.
+ */
+size_t b200q_workspace_bytes(int op, int M, int N, int K);
+
+/*
+ * Name of the kernel family the library would run for this problem, e.g.
+ * "umma_i8_128xN" — the counterpart of `select_path(...)` in
+ * nanovllm/quantization/csrc/w8a8_gemm.cpp:51-54 and
+ * int8_weight_only_gemm.cpp:40-43.  Never NULL.
+ */
+const char* b200q_select_path(int op, int M, int N, int K);
+
+/* Text for a return code.  Never NULL. */
+const char* b200q_strerror(int code);
+
+/* cudaError_t of the most recent failing CUDA call made by this library (0 if none). */
+int b200q_last_cuda_error(void);
+
+/*
+ * Reads (synchronously, small D2H copy) and clears the device-side status word
+ * of the current device.  0 = no kernel gave up a bounded wait since the last
+ * read.  Non-zero encodes which wait gave up.  Meant for tests and post-mortems,
+ * not for the hot path.
+ */
+int b200q_device_status(void);
+
+/* Library/ABI version (B200Q_VERSION). */
+int b200q_version(void);
+
+/*
+ * Test hook: force a kernel family (B200Q_PATH_*) for the GEMM entry points, or
+ * B200Q_PATH_AUTO to restore the built-in choice.  A family that cannot run the
+ * given problem makes the call return B200Q_ERR_UNSUPPORTED_SHAPE.  Returns the
+ * previous setting.  The reference exposes the same kind of switch through the
+ * NANOVLLM_INT8_BACKEND / NANOVLLM_W8A8_BACKEND variables
+ * (nanovllm/quantization/cuda.py:46-53).
+ */
+int b200q_debug_force_path(int path);
+
+/* Test hook: number of kernels this library has launched in this process. */
+uint64_t b200q_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

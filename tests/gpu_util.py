@@ -1,0 +1,29 @@
+"""Helpers of the GPU parity tests."""
+import contextlib
+
+import torch
+
+import tiny_vllm_b200  # noqa: F401
+from tiny_vllm_b200 import _lib
+
+PATHS = {"simt": _lib.PATH_SIMT_STREAM, "umma": _lib.PATH_UMMA, "umma_swap": _lib.PATH_UMMA_SWAP}
+
+
+@contextlib.contextmanager
+def forced_path(name):
+    """Runs the body with one kernel family forced (``None`` = the library's own choice)."""
+    L = _lib.lib()
+    prev = L.b200q_debug_force_path(PATHS[name] if name else _lib.PATH_AUTO)
+    try:
+        yield
+    finally:
+        L.b200q_debug_force_path(prev)
+
+
+def device_status_ok():
+    torch.cuda.synchronize()
+    return _lib.lib().b200q_device_status() == 0
+
+
+def bits(t: torch.Tensor) -> torch.Tensor:
+    return t.contiguous().view(torch.int16) if t.element_size() == 2 else t

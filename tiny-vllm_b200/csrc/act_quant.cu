@@ -1,0 +1,176 @@
+// Per-token dynamic int8 quantisation of activations, one pass over HBM.
+//
+//   a_scale[m] = max(absmax_k(x[m,k]) / 127, 1e-8)
+//   xq[m,k]    = clamp(rint(x[m,k] / a_scale[m]), -127, 127)
+//
+// Same arithmetic, operation by operation, as
+// nanovllm/quantization/utils.py:28-32 (fp32 absmax, IEEE division by 127, clamp_min,
+// IEEE division of every element by the scale, round-half-even, clamp, cast), so the
+// int8 codes and the scales are bit-identical to that function.
+//
+// A row is owned by a group of G threads (one warp, or one 256-thread CTA for long
+// rows).  Each thread keeps its part of the row in registers (128-bit loads), the
+// group reduces the absolute maximum with warp shuffles, and every thread then
+// converts and stores its elements as packed 64-bit words: x is read once and xq
+// written once (3 bytes of traffic per element for 16-bit inputs).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "common.h"
+
+namespace b200q {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t u);
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
+  // bf16 -> fp32 is a 16-bit shift
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
+  return __half22float2(*reinterpret_cast<__half2*>(&u));
+}
+
+__device__ __forceinline__ float absmax4(float m, const float2 a, const float2 b) {
+  return fmaxf(fmaxf(m, fmaxf(fabsf(a.x), fabsf(a.y))), fmaxf(fabsf(b.x), fabsf(b.y)));
+}
+
+__device__ __forceinline__ uint32_t quant1(float v, float scale) {
+  int q = __float2int_rn(__fdiv_rn(v, scale));  // round half to even
+  q = max(-127, min(127, q));
+  return static_cast<uint32_t>(q) & 0xFFu;
+}
+
+template <typename T>
+__device__ __forceinline__ uint2 quant8(const uint4 raw, float scale) {
+  const float2 a = unpack2<T>(raw.x), b = unpack2<T>(raw.y), c = unpack2<T>(raw.z),
+               d = unpack2<T>(raw.w);
+  uint2 o;
+  o.x = quant1(a.x, scale) | (quant1(a.y, scale) << 8) | (quant1(b.x, scale) << 16) |
+        (quant1(b.y, scale) << 24);
+  o.y = quant1(c.x, scale) | (quant1(c.y, scale) << 8) | (quant1(d.x, scale) << 16) |
+        (quant1(d.y, scale) << 24);
+  return o;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+
+// G threads per row (32 or 256), CHUNKS 16-byte chunks per thread held in registers.
+// Requires K <= G * 8 * CHUNKS.
+template <typename T, int G, int CHUNKS>
+__global__ void __launch_bounds__(256)
+act_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ xq,
+                      float* __restrict__ a_scales, int M, int K) {
+  constexpr int kRowsPerBlock = 256 / G;
+  const int g = threadIdx.x / G;  // row group inside the block
+  const int t = threadIdx.x % G;  // thread inside the group
+  const int row = blockIdx.x * kRowsPerBlock + g;
+  __shared__ float red[8];
+  const bool active = row < M;
+  const int nchunk = K >> 3;  // 8 elements per 16-byte chunk
+
+  uint4 raw[CHUNKS];
+  float amax = 0.f;
+  if (active) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int idx = c * G + t;
+      raw[c] = idx < nchunk ? __ldg(src + idx) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      amax = absmax4(amax, unpack2<T>(raw[c].x), unpack2<T>(raw[c].y));
+      amax = absmax4(amax, unpack2<T>(raw[c].z), unpack2<T>(raw[c].w));
+    }
+  }
+  amax = warp_max(amax);
+  if (G > 32) {
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    float m = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+    amax = m;
+  }
+  if (!active) return;
+  const float scale = fmaxf(__fdiv_rn(amax, 127.0f), 1e-8f);
+  if (t == 0) a_scales[row] = scale;
+  uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<size_t>(row) * K);
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int idx = c * G + t;
+    if (idx < nchunk) dst[idx] = quant8<T>(raw[c], scale);
+  }
+}
+
+// Any K: one 256-thread CTA per row, the row is read twice (the second read hits L2).
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_quant_long_rows_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ xq,
+                           float* __restrict__ a_scales, int M, int K) {
+  const int row = blockIdx.x;
+  __shared__ float red[8];
+  const int nchunk = K >> 3;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx);
+  float amax = 0.f;
+  for (int idx = threadIdx.x; idx < nchunk; idx += 256) {
+    const uint4 r = __ldg(src + idx);
+    amax = absmax4(amax, unpack2<T>(r.x), unpack2<T>(r.y));
+    amax = absmax4(amax, unpack2<T>(r.z), unpack2<T>(r.w));
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  float m = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+  const float scale = fmaxf(__fdiv_rn(m, 127.0f), 1e-8f);
+  if (threadIdx.x == 0) a_scales[row] = scale;
+  uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<size_t>(row) * K);
+  for (int idx = threadIdx.x; idx < nchunk; idx += 256)
+    dst[idx] = quant8<T>(__ldg(src + idx), scale);
+}
+
+template <typename T>
+cudaError_t launch_typed(const T* x, int64_t ldx, int8_t* xq, float* a_scales, int M, int K,
+                         cudaStream_t s) {
+  const int warp_rows_grid = (M + 7) / 8;  // 8 warps (rows) per 256-thread block
+  if (K <= 32 * 8 * 2) {
+    act_quant_rows_kernel<T, 32, 2><<<warp_rows_grid, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+  } else if (K <= 32 * 8 * 4) {
+    act_quant_rows_kernel<T, 32, 4><<<warp_rows_grid, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+  } else if (K <= 32 * 8 * 8) {
+    act_quant_rows_kernel<T, 32, 8><<<warp_rows_grid, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+  } else if (K <= 32 * 8 * 16) {
+    act_quant_rows_kernel<T, 32, 16><<<warp_rows_grid, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+  } else if (K <= 256 * 8 * 8) {
+    act_quant_rows_kernel<T, 256, 8><<<M, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+  } else {
+    act_quant_long_rows_kernel<T><<<M, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_act_quant(const void* x, int64_t ldx, int x_dtype, int8_t* xq, float* a_scales,
+                             int M, int K, cudaStream_t stream) {
+  cudaError_t e;
+  if (x_dtype == B200Q_DTYPE_BF16) {
+    e = launch_typed(reinterpret_cast<const __nv_bfloat16*>(x), ldx, xq, a_scales, M, K, stream);
+  } else {
+    e = launch_typed(reinterpret_cast<const __half*>(x), ldx, xq, a_scales, M, K, stream);
+  }
+  if (e == cudaSuccess) count_launch();
+  return e;
+}
+
+}  // namespace b200q

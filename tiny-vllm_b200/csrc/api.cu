@@ -1,0 +1,307 @@
+// C ABI of libb200q: argument validation, kernel-family choice, launches.
+// Nothing here allocates device memory, synchronises, or falls back to a CPU path.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <climits>
+#include <cstdint>
+
+#include "common.h"
+
+namespace b200q {
+
+// Device-side status word: a kernel whose bounded wait gave up writes a non-zero code here.
+__device__ int g_device_status = 0;
+
+namespace {
+std::atomic<int> g_last_cuda_error{0};
+std::atomic<uint64_t> g_launches{0};
+std::atomic<int> g_forced_path{B200Q_PATH_AUTO};
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+  std::atomic<int> ready{0};
+  int cc_major = 0;
+  int sms = 0;
+  int* status_ptr = nullptr;
+};
+DeviceInfo g_dev[kMaxDevices];
+
+DeviceInfo* device_info() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  DeviceInfo& d = g_dev[dev];
+  if (d.ready.load(std::memory_order_acquire) == 0) {
+    int major = 0, sms = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    void* p = nullptr;
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&p, g_device_status);
+    if (e != cudaSuccess) {
+      note_cuda_error(e);
+      return nullptr;
+    }
+    d.cc_major = major;
+    d.sms = sms;
+    d.status_ptr = static_cast<int*>(p);
+    d.ready.store(1, std::memory_order_release);
+  }
+  return &d;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_dims(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return B200Q_ERR_BAD_SHAPE;
+  if (static_cast<long long>(M) * N > INT_MAX || static_cast<long long>(M) * K > INT_MAX ||
+      static_cast<long long>(N) * K > INT_MAX)
+    return B200Q_ERR_BAD_SHAPE;
+  if ((K % 16) != 0) return B200Q_ERR_UNSUPPORTED_SHAPE;
+  return B200Q_OK;
+}
+
+// Kernel family for a W8A8 problem when nothing is forced.
+int auto_path_w8a8(int M, int N, int K) {
+  (void)N;
+  (void)K;
+  if (M <= 4) return B200Q_PATH_SIMT_STREAM;
+  if (M <= 256) return B200Q_PATH_UMMA_SWAP;
+  return B200Q_PATH_UMMA;
+}
+
+int resolve_path(int op, int M, int N, int K) {
+  const int forced = g_forced_path.load();
+  if (op == B200Q_OP_W8A16) return B200Q_PATH_SIMT_STREAM;
+  if (forced != B200Q_PATH_AUTO) return forced;
+  return auto_path_w8a8(M, N, K);
+}
+
+int run_w8a8(GemmArgs& a) {
+  DeviceInfo* d = device_info();
+  if (d == nullptr) return B200Q_ERR_LAUNCH;
+  if (d->cc_major != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+  a.status = d->status_ptr;
+  const int path = resolve_path(B200Q_OP_W8A8, a.M, a.N, a.K);
+  if (path == B200Q_PATH_SIMT_STREAM) {
+    cudaError_t e = launch_w8a8_simt(a);
+    if (e != cudaSuccess) {
+      note_cuda_error(e);
+      return B200Q_ERR_LAUNCH;
+    }
+    return B200Q_OK;
+  }
+  if (path == B200Q_PATH_UMMA || path == B200Q_PATH_UMMA_SWAP) {
+    UmmaPlan plan;
+    if (!umma_make_plan(B200Q_OP_W8A8, a.M, a.N, a.K, path == B200Q_PATH_UMMA_SWAP, &plan))
+      return B200Q_ERR_UNSUPPORTED_SHAPE;
+    return launch_w8a8_umma(a, plan);
+  }
+  return B200Q_ERR_BAD_ARGUMENT;
+}
+
+}  // namespace
+
+int sm_count() {
+  DeviceInfo* d = device_info();
+  return d != nullptr && d->sms > 0 ? d->sms : 148;
+}
+
+void note_cuda_error(cudaError_t e) { g_last_cuda_error.store(static_cast<int>(e)); }
+void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n)); }
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_act_quant_i8(const void* x, int64_t ldx, int x_dtype, int8_t* xq, float* a_scales, int M,
+                       int K, void* stream) {
+  if (x == nullptr || xq == nullptr || a_scales == nullptr) return B200Q_ERR_NULL_POINTER;
+  if (M <= 0 || K <= 0 || static_cast<long long>(M) * K > INT_MAX) return B200Q_ERR_BAD_SHAPE;
+  if (x_dtype != B200Q_DTYPE_F16 && x_dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  if ((K % 16) != 0 || ldx < K || (ldx % 8) != 0) return B200Q_ERR_UNSUPPORTED_SHAPE;
+  if (!aligned16(x) || !aligned16(xq) || (reinterpret_cast<uintptr_t>(a_scales) & 3u) != 0)
+    return B200Q_ERR_MISALIGNED;
+  DeviceInfo* d = device_info();
+  if (d == nullptr) return B200Q_ERR_LAUNCH;
+  if (d->cc_major != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+  cudaError_t e =
+      launch_act_quant(x, ldx, x_dtype, xq, a_scales, M, K, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  return B200Q_OK;
+}
+
+int b200q_w8a8_gemm(const int8_t* xq, const float* a_scales, const int8_t* qweight,
+                    const float* w_scales, const void* bias, void* y, int M, int N, int K,
+                    int out_dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  if (xq == nullptr || a_scales == nullptr || qweight == nullptr || w_scales == nullptr ||
+      y == nullptr)
+    return B200Q_ERR_NULL_POINTER;
+  if (int rc = check_dims(M, N, K)) return rc;
+  if (out_dtype != B200Q_DTYPE_F16 && out_dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  if (!aligned16(xq) || !aligned16(qweight) || !aligned16(y) || !aligned16(w_scales) ||
+      (reinterpret_cast<uintptr_t>(a_scales) & 3u) != 0 ||
+      (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 1u) != 0) ||
+      (workspace != nullptr && !aligned16(workspace)))
+    return B200Q_ERR_MISALIGNED;
+  GemmArgs a{};
+  a.x = xq;
+  a.w = qweight;
+  a.a_scales = a_scales;
+  a.w_scales = w_scales;
+  a.bias = bias;
+  a.y = y;
+  a.acc_out = nullptr;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.dtype = out_dtype;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return run_w8a8(a);
+}
+
+int b200q_w8a8_gemm_i32(const int8_t* xq, const int8_t* qweight, int32_t* acc, int M, int N, int K,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  if (xq == nullptr || qweight == nullptr || acc == nullptr) return B200Q_ERR_NULL_POINTER;
+  if (int rc = check_dims(M, N, K)) return rc;
+  if (!aligned16(xq) || !aligned16(qweight) || !aligned16(acc) ||
+      (workspace != nullptr && !aligned16(workspace)))
+    return B200Q_ERR_MISALIGNED;
+  GemmArgs a{};
+  a.x = xq;
+  a.w = qweight;
+  a.acc_out = acc;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.dtype = B200Q_DTYPE_BF16;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return run_w8a8(a);
+}
+
+int b200q_w8a16_gemm(const void* x, const int8_t* qweight, const float* scales, const void* bias,
+                     void* y, int M, int N, int K, int x_dtype, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  if (x == nullptr || qweight == nullptr || scales == nullptr || y == nullptr)
+    return B200Q_ERR_NULL_POINTER;
+  if (int rc = check_dims(M, N, K)) return rc;
+  if (x_dtype != B200Q_DTYPE_F16 && x_dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  if (!aligned16(x) || !aligned16(qweight) || !aligned16(y) || !aligned16(scales) ||
+      (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 1u) != 0) ||
+      (workspace != nullptr && !aligned16(workspace)))
+    return B200Q_ERR_MISALIGNED;
+  DeviceInfo* d = device_info();
+  if (d == nullptr) return B200Q_ERR_LAUNCH;
+  if (d->cc_major != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+  GemmArgs a{};
+  a.x = x;
+  a.w = qweight;
+  a.w_scales = scales;
+  a.bias = bias;
+  a.y = y;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.dtype = x_dtype;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.status = d->status_ptr;
+  a.stream = static_cast<cudaStream_t>(stream);
+  cudaError_t e = launch_w8a16_simt(a);
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  return B200Q_OK;
+}
+
+size_t b200q_workspace_bytes(int op, int M, int N, int K) {
+  if (op != B200Q_OP_W8A8) return 0;
+  if (check_dims(M, N, K) != B200Q_OK) return 0;
+  const int path = resolve_path(op, M, N, K);
+  if (path != B200Q_PATH_UMMA && path != B200Q_PATH_UMMA_SWAP) return 0;
+  UmmaPlan plan;
+  if (!umma_make_plan(op, M, N, K, path == B200Q_PATH_UMMA_SWAP, &plan)) return 0;
+  return plan.ws_bytes;
+}
+
+const char* b200q_select_path(int op, int M, int N, int K) {
+  if (op == B200Q_OP_ACT_QUANT) return K <= 4096 ? "act_quant_warp_per_row" : "act_quant_cta_per_row";
+  if (op != B200Q_OP_W8A8 && op != B200Q_OP_W8A16) return "invalid_op";
+  if (check_dims(M, N, K) != B200Q_OK) return "unsupported_shape";
+  const int path = resolve_path(op, M, N, K);
+  if (op == B200Q_OP_W8A16) return "simt_stream_w8a16";
+  switch (path) {
+    case B200Q_PATH_SIMT_STREAM:
+      return "simt_stream_dp4a";
+    case B200Q_PATH_UMMA:
+      return "umma_i8_tokens128";
+    case B200Q_PATH_UMMA_SWAP:
+      return "umma_i8_channels128_splitk";
+    default:
+      return "invalid_path";
+  }
+}
+
+const char* b200q_strerror(int code) {
+  switch (code) {
+    case B200Q_OK:
+      return "ok";
+    case B200Q_ERR_NULL_POINTER:
+      return "a required pointer is NULL";
+    case B200Q_ERR_BAD_SHAPE:
+      return "M, N or K is not positive or too large";
+    case B200Q_ERR_UNSUPPORTED_SHAPE:
+      return "unsupported shape (K must be a multiple of 16; row pitch rules)";
+    case B200Q_ERR_MISALIGNED:
+      return "a pointer is not sufficiently aligned (16 bytes)";
+    case B200Q_ERR_WORKSPACE:
+      return "workspace missing or smaller than b200q_workspace_bytes()";
+    case B200Q_ERR_UNSUPPORTED_ARCH:
+      return "device is not compute capability 10.x (B200)";
+    case B200Q_ERR_LAUNCH:
+      return "a CUDA call failed (see b200q_last_cuda_error)";
+    case B200Q_ERR_BAD_ARGUMENT:
+      return "unknown op, dtype or path id";
+    case B200Q_ERR_DEVICE_TIMEOUT:
+      return "a bounded device-side wait gave up";
+    default:
+      return "unknown error code";
+  }
+}
+
+int b200q_last_cuda_error(void) { return g_last_cuda_error.load(); }
+
+int b200q_device_status(void) {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int));
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return -1;
+  }
+  if (v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+  }
+  return v;
+}
+
+int b200q_version(void) { return B200Q_VERSION; }
+
+int b200q_debug_force_path(int path) {
+  if (path < B200Q_PATH_AUTO || path > B200Q_PATH_UMMA_SWAP) return -1;
+  return g_forced_path.exchange(path);
+}
+
+uint64_t b200q_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

@@ -1,0 +1,68 @@
+// Internal declarations shared by the translation units of libb200q.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/b200q.h"
+
+namespace b200q {
+
+// One linear-layer problem, in the vocabulary of the layer: M tokens, K input
+// features, N output channels.
+struct GemmArgs {
+  const void* x;          // int8 [M,K] (W8A8) or f16/bf16 [M,K] (W8A16)
+  const int8_t* w;        // int8 [N,K]
+  const float* a_scales;  // fp32 [M]  (W8A8 only)
+  const float* w_scales;  // fp32 [N]
+  const void* bias;       // [N] in `dtype`, or nullptr
+  void* y;                // [M,N] in `dtype`            (nullptr in int32 mode)
+  int32_t* acc_out;       // [M,N] raw accumulators      (int32 mode only)
+  int M, N, K;
+  int dtype;              // B200Q_DTYPE_*
+  void* workspace;
+  size_t workspace_bytes;
+  int* status;            // device status word of the current device
+  cudaStream_t stream;
+};
+
+// Tiling of one problem onto the tcgen05 kernel.  "A side" is the operand that
+// fills the 128 rows of the UMMA tile, "B side" the one that fills its columns.
+struct UmmaPlan {
+  int swap;          // 0: A = tokens, B = channels; 1: A = channels, B = tokens
+  int rows_a, rows_b;
+  int bn;            // B-side tile (UMMA N), multiple of 32, <= 256
+  int tiles_a, tiles_b;
+  int k_blocks;      // ceil(K_bytes / 128)
+  int splits;        // split-K factor
+  int kb_per_split;
+  int stages;        // shared-memory ring depth
+  int tmem_cols;     // power of two >= 2 * bn
+  int grid;          // CTAs launched (persistent)
+  size_t smem_bytes;
+  size_t ws_bytes;   // counters + split-K partials (0 when splits == 1)
+};
+
+constexpr size_t kCounterBytes = 16384;  // zero-initialised tile counters at workspace start
+
+// Number of SMs of the current device (cached).
+int sm_count();
+
+// act_quant.cu
+cudaError_t launch_act_quant(const void* x, int64_t ldx, int x_dtype, int8_t* xq, float* a_scales,
+                             int M, int K, cudaStream_t stream);
+
+// gemm_simt.cu
+cudaError_t launch_w8a8_simt(const GemmArgs& a);
+cudaError_t launch_w8a16_simt(const GemmArgs& a);
+
+// gemm_umma.cu
+bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan);
+// Returns a B200Q_* code.
+int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan);
+
+void note_cuda_error(cudaError_t e);
+void count_launch(int n = 1);
+
+}  // namespace b200q

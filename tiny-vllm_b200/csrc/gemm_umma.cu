@@ -1,0 +1,602 @@
+// W8A8 GEMM on the 5th-generation tensor cores (tcgen05) of sm_100a.
+//
+// One persistent, warp-specialised kernel:
+//   warp 0      TMA producer: streams 128-byte-wide K blocks of both operands into a
+//               shared-memory ring (128-byte swizzle), one mbarrier per stage.
+//   warp 1      UMMA issuer: tcgen05.mma kind::i8 (int8 x int8 -> int32), accumulators
+//               in TMEM, double-buffered so that the epilogue of tile i overlaps the
+//               main loop of tile i+1.
+//   warps 2-5   epilogue: tcgen05.ld -> (acc * a_scale) * w_scale + bias -> f16/bf16
+//               -> global, or raw int32, or split-K partials + last-arriver reduction.
+//
+// The operand on the 128-row side of the UMMA tile ("A side") is the activation
+// matrix for prefill-shaped problems and the weight matrix for decode-shaped ones
+// ("swap"), where the few tokens become the N extent of the instruction and K is
+// split over CTAs so that the whole GPU streams the weights.
+//
+// Arithmetic follows nanovllm/quantization/csrc/w8a8_gemm.cu:165-183 (exact int32
+// accumulation) and :387-390 (float(acc) * a_scale * w_scale + bias, cast).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.h"
+#include "ptx_sm100.cuh"
+
+namespace b200q {
+namespace {
+
+constexpr int kTileA = 128;       // UMMA M
+constexpr int kBlockK = 128;      // bytes of K per pipeline stage = one swizzle row
+constexpr int kUmmaK = 32;        // bytes of K per tcgen05.mma kind::i8
+constexpr int kThreads = 192;     // 6 warps
+constexpr int kEpiThreads = 128;  // warps 2..5
+constexpr int kMaxStages = 8;
+constexpr int kMaxSmem = 227 * 1024;
+
+enum { OUT_SCALED = 0, OUT_I32 = 1 };
+
+struct KernelParams {
+  int rows_a, rows_b;
+  int bn;
+  int tiles_a, tiles_b;
+  int k_blocks, splits, kb_per_split;
+  int stages;
+  int tmem_cols;
+  int swap;
+  int n_channels;          // leading dimension of the output
+  int n_tokens;
+  const float* a_scales;   // per token
+  const float* w_scales;   // per channel
+  const void* bias;        // per channel, OutT
+  void* out;               // OutT [M,N] or int32 [M,N]
+  int32_t* partials;
+  unsigned int* counters;
+  int* status;
+};
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) {
+  return __half2float(v);
+}
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  T a = from_float<T>(lo), b = from_float<T>(hi);
+  uint16_t ua = *reinterpret_cast<uint16_t*>(&a), ub = *reinterpret_cast<uint16_t*>(&b);
+  return static_cast<uint32_t>(ua) | (static_cast<uint32_t>(ub) << 16);
+}
+
+// (acc * a_scale) * w_scale + bias with one rounding per operation, as the
+// reference epilogue is written (no fused multiply-add).
+__device__ __forceinline__ float scale_acc(int acc, float a_s, float w_s, float b) {
+  return __fadd_rn(__fmul_rn(__fmul_rn(static_cast<float>(acc), a_s), w_s), b);
+}
+
+// Writes the 32 accumulators this thread holds for columns [c0, c0+32) of its row.
+template <typename OutT, int MODE>
+__device__ __forceinline__ void emit_chunk(const KernelParams& p, int tile_a, int tile_b,
+                                           int row_in_tile, int c0, const uint32_t (&v)[32]) {
+  const int row_a = tile_a * kTileA + row_in_tile;
+  const int col_b0 = tile_b * p.bn + c0;
+  if (row_a >= p.rows_a || col_b0 >= p.rows_b) return;
+  const int N = p.n_channels;
+  if (!p.swap) {
+    // row = token, columns = channels: the thread owns 32 consecutive outputs of a row.
+    const size_t off = static_cast<size_t>(row_a) * N + col_b0;
+    const bool full = (col_b0 + 32 <= p.rows_b);
+    if (MODE == OUT_I32) {
+      int32_t* dst = reinterpret_cast<int32_t*>(p.out) + off;
+      if (full && (N & 3) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+        for (int j = 0; j < 32 && col_b0 + j < p.rows_b; ++j) dst[j] = static_cast<int32_t>(v[j]);
+      }
+    } else {
+      const float a_s = __ldg(p.a_scales + row_a);
+      const OutT* bias = reinterpret_cast<const OutT*>(p.bias);
+      OutT* dst = reinterpret_cast<OutT*>(p.out) + off;
+      if (full && (N & 7) == 0) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 ws = __ldg(reinterpret_cast<const float4*>(p.w_scales + col_b0 + j));
+          float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+          if (bias != nullptr) {
+            b0 = to_float<OutT>(bias[col_b0 + j]);
+            b1 = to_float<OutT>(bias[col_b0 + j + 1]);
+            b2 = to_float<OutT>(bias[col_b0 + j + 2]);
+            b3 = to_float<OutT>(bias[col_b0 + j + 3]);
+          }
+          packed[j / 2] = pack2<OutT>(scale_acc(static_cast<int>(v[j]), a_s, ws.x, b0),
+                                      scale_acc(static_cast<int>(v[j + 1]), a_s, ws.y, b1));
+          packed[j / 2 + 1] = pack2<OutT>(scale_acc(static_cast<int>(v[j + 2]), a_s, ws.z, b2),
+                                          scale_acc(static_cast<int>(v[j + 3]), a_s, ws.w, b3));
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(dst) + j) =
+              make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+      } else {
+        for (int j = 0; j < 32 && col_b0 + j < p.rows_b; ++j) {
+          const float b = bias != nullptr ? to_float<OutT>(bias[col_b0 + j]) : 0.f;
+          dst[j] = from_float<OutT>(
+              scale_acc(static_cast<int>(v[j]), a_s, __ldg(p.w_scales + col_b0 + j), b));
+        }
+      }
+    }
+  } else {
+    // row = channel, columns = tokens: consecutive lanes write consecutive channels.
+    if (MODE == OUT_I32) {
+      int32_t* dst = reinterpret_cast<int32_t*>(p.out);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int tok = col_b0 + j;
+        if (tok < p.rows_b) dst[static_cast<size_t>(tok) * N + row_a] = static_cast<int32_t>(v[j]);
+      }
+    } else {
+      const float w_s = __ldg(p.w_scales + row_a);
+      const OutT* bias = reinterpret_cast<const OutT*>(p.bias);
+      const float b = bias != nullptr ? to_float<OutT>(bias[row_a]) : 0.f;
+      OutT* dst = reinterpret_cast<OutT*>(p.out);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int tok = col_b0 + j;
+        if (tok < p.rows_b) {
+          const float a_s = __ldg(p.a_scales + tok);
+          dst[static_cast<size_t>(tok) * N + row_a] =
+              from_float<OutT>(scale_acc(static_cast<int>(v[j]), a_s, w_s, b));
+        }
+      }
+    }
+  }
+}
+
+template <typename OutT, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b, const KernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // The swizzled operand tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t stage_bytes = kTileA * kBlockK + p.bn * kBlockK;
+  uint8_t* ctrl = smem + static_cast<size_t>(p.stages) * stage_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* tfull_bar = empty_bar + kMaxStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = ptx::smem_u32(smem);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(full_bar + s), 1);
+      ptx::mbar_init(ptx::smem_u32(empty_bar + s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(ptx::smem_u32(tfull_bar + b), 1);
+      ptx::mbar_init(ptx::smem_u32(tempty_bar + b), kEpiThreads);
+    }
+    *abort_flag = 0;
+    last_flag[0] = 0;
+    last_flag[1] = 0;
+    ptx::fence_mbar_init();
+    ptx::tma_prefetch_desc(&tmap_a);
+    ptx::tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), static_cast<uint32_t>(p.tmem_cols));
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_items = p.tiles_a * p.tiles_b * p.splits;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------ TMA producer
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const int split = item % p.splits;
+        const int t = item / p.splits;
+        const int tile_a = t % p.tiles_a;
+        const int tile_b = t / p.tiles_a;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(empty_bar + stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = ptx::smem_u32(full_bar + stage);
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + kTileA * kBlockK;
+          ptx::mbar_arrive_expect_tx(bar, stage_bytes);
+          ptx::tma_load_2d(sa, &tmap_a, bar, kb * kBlockK, tile_a * kTileA);
+          ptx::tma_load_2d(sb, &tmap_b, bar, kb * kBlockK, tile_b * p.bn);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------- UMMA issuer
+      const uint32_t idesc = ptx::umma_idesc(2u, 1u, kTileA, static_cast<uint32_t>(p.bn));
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++it) {
+        const int split = item % p.splits;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        const int buf = it & 1;
+        const uint32_t tphase = static_cast<uint32_t>(it >> 1) & 1u;
+        if (!ptx::mbar_wait(ptx::smem_u32(tempty_bar + buf), tphase ^ 1u, abort_flag)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.bn);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(full_bar + stage), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + kTileA * kBlockK;
+          const uint64_t a_desc = ptx::umma_desc_k_sw128(sa);
+          const uint64_t b_desc = ptx::umma_desc_k_sw128(sb);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // advancing K by 32 bytes inside the swizzled row = +2 in 16-byte units
+            ptx::umma_i8_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                            (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          ptx::umma_commit(ptx::smem_u32(empty_bar + stage));
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) ptx::umma_commit(ptx::smem_u32(tfull_bar + buf));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const int row_in_tile = quarter * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;
+    int it = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
+      const int split = item % p.splits;
+      const int t = item / p.splits;
+      const int tile_a = t % p.tiles_a;
+      const int tile_b = t / p.tiles_a;
+      const int buf = it & 1;
+      const uint32_t tphase = static_cast<uint32_t>(it >> 1) & 1u;
+      if (!ptx::mbar_wait(ptx::smem_u32(tfull_bar + buf), tphase, abort_flag)) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * p.bn);
+      if (p.splits == 1) {
+        for (int c0 = 0; c0 < p.bn; c0 += 32) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c0, v);
+          ptx::tmem_ld_wait();
+          emit_chunk<OutT, MODE>(p, tile_a, tile_b, row_in_tile, c0, v);
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(ptx::smem_u32(tempty_bar + buf));
+      } else {
+        // split-K: park the partial tile, the last CTA to arrive sums all of them.
+        int32_t* mine = p.partials +
+                        (static_cast<size_t>(t) * p.splits + split) * p.bn * kTileA + row_in_tile;
+        for (int c0 = 0; c0 < p.bn; c0 += 32) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c0, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            __stcg(mine + static_cast<size_t>(c0 + j) * kTileA, static_cast<int32_t>(v[j]));
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(ptx::smem_u32(tempty_bar + buf));
+        __threadfence();
+        ptx::named_bar_sync(1, kEpiThreads);
+        if (epi_tid == 0) {
+          const unsigned int old = atomicAdd(p.counters + t, 1u);
+          const int last = (old == static_cast<unsigned int>(p.splits - 1));
+          if (last) p.counters[t] = 0u;  // every split has arrived: leave the counter clean
+          last_flag[it & 1] = last;
+        }
+        ptx::named_bar_sync(1, kEpiThreads);
+        if (last_flag[it & 1]) {
+          __threadfence();
+          const int32_t* base =
+              p.partials + static_cast<size_t>(t) * p.splits * p.bn * kTileA + row_in_tile;
+          for (int c0 = 0; c0 < p.bn; c0 += 32) {
+            uint32_t v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0u;
+            for (int s = 0; s < p.splits; ++s) {
+              const int32_t* src = base + static_cast<size_t>(s) * p.bn * kTileA;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                v[j] += static_cast<uint32_t>(__ldcg(src + static_cast<size_t>(c0 + j) * kTileA));
+            }
+            emit_chunk<OutT, MODE>(p, tile_a, tile_b, row_in_tile, c0, v);
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0) {
+    atomicCAS(p.status, 0, 0x100 | (static_cast<int>(blockIdx.x) << 12));
+  }
+}
+
+// ------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+    if (e == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(sym);
+    else note_cuda_error(e == cudaSuccess ? cudaErrorUnknown : e);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  uint64_t rows, kbytes;
+  uint32_t box_rows;
+  int device;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && kbytes == o.kbytes && box_rows == o.box_rows &&
+           device == o.device;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= k.kbytes * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+    h ^= (static_cast<size_t>(k.box_rows) << 8) ^ static_cast<size_t>(k.device);
+    return h;
+  }
+};
+
+// Descriptor of a dense row-major byte matrix [rows, kbytes], box = 128 bytes x box_rows,
+// 128-byte swizzle, zero fill outside the matrix.  Cached: encoding costs microseconds.
+bool get_tensor_map(const void* base, uint64_t rows, uint64_t kbytes, uint32_t box_rows,
+                    CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  MapKey key{base, rows, kbytes, box_rows, dev};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {kbytes, rows};
+  cuuint64_t strides[1] = {kbytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    note_cuda_error(cudaErrorInvalidValue);
+    return false;
+  }
+  {
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, m);
+  }
+  *out = m;
+  return true;
+}
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+int env_int(const char* name, int dflt) {
+  const char* s = std::getenv(name);
+  if (s == nullptr || *s == '\0') return dflt;
+  return std::atoi(s);
+}
+
+template <typename OutT, int MODE>
+cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp,
+                          const UmmaPlan& plan, cudaStream_t stream) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = w8a8_umma_kernel<OutT, MODE>;
+  if (dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  kern<<<plan.grid, kThreads, plan.smem_bytes, stream>>>(ta, tb, kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan) {
+  if (op != B200Q_OP_W8A8) return false;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 16) != 0) return false;
+  UmmaPlan pl{};
+  pl.swap = swap;
+  pl.rows_a = swap ? N : M;
+  pl.rows_b = swap ? M : N;
+  const int sms = sm_count();
+  pl.k_blocks = (K + kBlockK - 1) / kBlockK;
+  int bn = pl.rows_b >= 256 ? 256 : round_up(pl.rows_b, 32);
+  if (!swap && pl.rows_b >= 256) {
+    // Prefer the N tile that leaves the fewest idle SMs in the last wave.
+    const int ta = (pl.rows_a + kTileA - 1) / kTileA;
+    double best = 1e30;
+    for (int cand : {256, 128}) {
+      const int tiles = ta * ((pl.rows_b + cand - 1) / cand);
+      const int waves = (tiles + sms - 1) / sms;
+      // cost model: a wave costs its MMA time (proportional to cand) plus a fixed part
+      const double cost = waves * (cand + 48.0);
+      if (cost < best) {
+        best = cost;
+        bn = cand;
+      }
+    }
+  }
+  bn = env_int("B200Q_DEBUG_BN", bn);
+  if (bn < 32 || bn > 256 || (bn % 32) != 0) return false;
+  pl.bn = bn;
+  pl.tiles_a = (pl.rows_a + kTileA - 1) / kTileA;
+  pl.tiles_b = (pl.rows_b + bn - 1) / bn;
+  const long long tiles = static_cast<long long>(pl.tiles_a) * pl.tiles_b;
+  if (tiles > 1 << 22) return false;
+  int splits = 1;
+  if (tiles < sms) {
+    splits = static_cast<int>(sms / tiles);
+    // keep at least two K blocks per split and bound the partial-sum traffic
+    splits = std::min(splits, std::max(1, pl.k_blocks / 2));
+    splits = std::min(splits, 16);
+  }
+  splits = env_int("B200Q_DEBUG_SPLITS", splits);
+  if (splits < 1) splits = 1;
+  if (splits > pl.k_blocks) splits = pl.k_blocks;
+  pl.kb_per_split = (pl.k_blocks + splits - 1) / splits;
+  pl.splits = (pl.k_blocks + pl.kb_per_split - 1) / pl.kb_per_split;
+  if (pl.splits > 1 && tiles * sizeof(unsigned int) > kCounterBytes) return false;
+  const int stage_bytes = kTileA * kBlockK + bn * kBlockK;
+  int stages = (kMaxSmem - 1024 - 256) / stage_bytes;
+  stages = std::min(stages, kMaxStages);
+  stages = std::min(stages, std::max(2, pl.kb_per_split * 2));
+  pl.stages = stages;
+  pl.smem_bytes = static_cast<size_t>(stages) * stage_bytes + 1024 + 256;
+  int cols = 32;
+  while (cols < 2 * bn) cols *= 2;
+  pl.tmem_cols = cols;
+  const long long items = tiles * pl.splits;
+  pl.grid = static_cast<int>(std::min<long long>(items, sms));
+  pl.ws_bytes = pl.splits > 1
+                    ? kCounterBytes + static_cast<size_t>(tiles) * pl.splits * bn * kTileA * sizeof(int32_t)
+                    : 0;
+  *plan = pl;
+  return true;
+}
+
+int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
+  if (plan.ws_bytes > 0) {
+    if (a.workspace == nullptr || a.workspace_bytes < plan.ws_bytes) return B200Q_ERR_WORKSPACE;
+  }
+  const void* base_a = plan.swap ? static_cast<const void*>(a.w) : a.x;
+  const void* base_b = plan.swap ? a.x : static_cast<const void*>(a.w);
+  CUtensorMap ta, tb;
+  if (!get_tensor_map(base_a, plan.rows_a, a.K, kTileA, &ta)) return B200Q_ERR_LAUNCH;
+  if (!get_tensor_map(base_b, plan.rows_b, a.K, plan.bn, &tb)) return B200Q_ERR_LAUNCH;
+
+  KernelParams kp{};
+  kp.rows_a = plan.rows_a;
+  kp.rows_b = plan.rows_b;
+  kp.bn = plan.bn;
+  kp.tiles_a = plan.tiles_a;
+  kp.tiles_b = plan.tiles_b;
+  kp.k_blocks = plan.k_blocks;
+  kp.splits = plan.splits;
+  kp.kb_per_split = plan.kb_per_split;
+  kp.stages = plan.stages;
+  kp.tmem_cols = plan.tmem_cols;
+  kp.swap = plan.swap;
+  kp.n_channels = a.N;
+  kp.n_tokens = a.M;
+  kp.a_scales = a.a_scales;
+  kp.w_scales = a.w_scales;
+  kp.bias = a.bias;
+  kp.out = a.acc_out != nullptr ? static_cast<void*>(a.acc_out) : a.y;
+  kp.counters = reinterpret_cast<unsigned int*>(a.workspace);
+  kp.partials = plan.ws_bytes > 0
+                    ? reinterpret_cast<int32_t*>(static_cast<uint8_t*>(a.workspace) + kCounterBytes)
+                    : nullptr;
+  kp.status = a.status;
+
+  cudaError_t e;
+  if (a.acc_out != nullptr) {
+    e = launch_kernel<__nv_bfloat16, OUT_I32>(ta, tb, kp, plan, a.stream);
+  } else if (a.dtype == B200Q_DTYPE_BF16) {
+    e = launch_kernel<__nv_bfloat16, OUT_SCALED>(ta, tb, kp, plan, a.stream);
+  } else {
+    e = launch_kernel<__half, OUT_SCALED>(ta, tb, kp, plan, a.stream);
+  }
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  count_launch();
+  return B200Q_OK;
+}
+
+}  // namespace b200q

@@ -1,0 +1,226 @@
+"""Python entry points of the quantized-linear kernels.
+
+Counterpart of ``nanovllm/quantization/cuda.py`` in the reference: the same
+public functions (``apply_int8_weight_only_linear`` — reference lines 303-366,
+``apply_w8a8_linear`` — lines 468-504) with the same argument meaning and the
+same input checks (reference lines 21-33, 225-258, 369-432).  Differences, all
+deliberate:
+
+* one backend — the sm_100a library behind ``include/b200q.h``; the backend
+  environment switches of the reference are gone;
+* no Python/CPU fallback: an input the kernels cannot take raises
+  ``RuntimeError`` where the reference would silently run dequantize + matmul;
+* kernels run on ``torch.cuda.current_stream()`` so CUDA-graph capture records
+  them (the reference launches on the legacy default stream).
+"""
+from __future__ import annotations
+
+import os
+import threading
+
+import torch
+
+from .. import _lib
+
+_DTYPE_IDS = {torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16}
+_DEFAULT_WORKSPACE_BYTES = 64 << 20
+
+_ws_lock = threading.Lock()
+_workspaces: dict[int, torch.Tensor] = {}
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
+    """Zero-filled scratch buffer shared by every call on ``device``.
+
+    The split-K kernels keep their tile counters in it and leave them at zero,
+    so a single buffer serves all layers as long as calls are stream-ordered
+    (they are: one stream per model runner).  It is allocated once, large enough
+    for the shapes of a decode step, so that nothing is allocated while a CUDA
+    graph is being captured.
+    """
+    if nbytes == 0:
+        return None
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is not None and ws.numel() >= nbytes:
+        return ws
+    with _ws_lock:
+        ws = _workspaces.get(idx)
+        if ws is None or ws.numel() < nbytes:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(
+                    f"b200q workspace of {nbytes} bytes requested during CUDA graph capture; "
+                    "run the shape once eagerly first or raise B200Q_WORKSPACE_BYTES")
+            want = max(nbytes, int(os.environ.get("B200Q_WORKSPACE_BYTES", _DEFAULT_WORKSPACE_BYTES)))
+            ws = torch.zeros(want, dtype=torch.uint8, device=torch.device("cuda", idx))
+            _workspaces[idx] = ws
+    return ws
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    if not torch.cuda.is_available() or not all(t.is_cuda for t in tensors):
+        raise RuntimeError(
+            "b200q kernels need CUDA tensors on a B200; there is no CPU implementation of this path")
+
+
+def select_path(op: int, M: int, N: int, K: int) -> str:
+    """Kernel family the library picks for a problem (reference: ``select_path`` of the
+    pybind modules, ``csrc/w8a8_gemm.cpp:51-54``)."""
+    return _lib.lib().b200q_select_path(op, M, N, K).decode()
+
+
+def quantize_activation_int8(x_2d: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-token dynamic int8 quantisation on the GPU (one kernel).
+
+    ``x_2d`` is ``[M, K]`` fp16/bf16 with unit inner stride.  Returns ``(x_q int8
+    [M, K], a_scales fp32 [M])``, bit-identical to the reference's
+    ``quantize_int8_per_row_dynamic`` (``nanovllm/quantization/utils.py:28-32``).
+    """
+    _require_cuda(x_2d)
+    if x_2d.dim() != 2 or x_2d.dtype not in _DTYPE_IDS:
+        raise RuntimeError("activation quantisation expects a 2-D float16/bfloat16 tensor")
+    if x_2d.stride(1) != 1 or x_2d.stride(0) < x_2d.shape[1] or x_2d.stride(0) % 8 != 0 \
+            or x_2d.data_ptr() % 16 != 0:
+        x_2d = x_2d.contiguous()
+    M, K = x_2d.shape
+    if M == 0:
+        return (torch.empty((0, K), dtype=torch.int8, device=x_2d.device),
+                torch.empty((0,), dtype=torch.float32, device=x_2d.device))
+    x_q = torch.empty((M, K), dtype=torch.int8, device=x_2d.device)
+    a_scales = torch.empty((M,), dtype=torch.float32, device=x_2d.device)
+    with torch.cuda.device(x_2d.device):
+        rc = _lib.lib().b200q_act_quant_i8(x_2d.data_ptr(), x_2d.stride(0), _DTYPE_IDS[x_2d.dtype],
+                                           x_q.data_ptr(), a_scales.data_ptr(), M, K,
+                                           _stream_ptr(x_2d.device))
+    _lib.check(rc, "b200q_act_quant_i8", f"M={M} K={K}")
+    return x_q, a_scales
+
+
+def _check_w8a16(x, qweight, scales, bias) -> None:
+    _require_cuda(x, qweight, scales)
+    if x.dtype not in _DTYPE_IDS or qweight.dtype != torch.int8 or scales.dtype != torch.float32:
+        raise RuntimeError("CUDA INT8 weight-only backend does not support the provided tensors")
+    if x.numel() == 0 or qweight.numel() == 0 or scales.numel() == 0:
+        raise RuntimeError("CUDA INT8 weight-only backend does not support the provided tensors")
+    if qweight.dim() != 2 or x.shape[-1] != qweight.shape[-1]:
+        raise RuntimeError(f"Incompatible shapes: x[-1]={x.shape[-1]} vs qweight[-1]={qweight.shape[-1]}")
+    if scales.dim() != 1 or scales.numel() != qweight.shape[0]:
+        raise RuntimeError("scales must be 1D with one value per output channel")
+    if bias is not None:
+        if bias.dim() != 1 or bias.numel() != qweight.shape[0]:
+            raise RuntimeError("bias must be 1D with one value per output channel")
+        if bias.dtype != x.dtype or not bias.is_cuda:
+            raise RuntimeError("bias must be a CUDA tensor of the activation dtype")
+
+
+def apply_int8_weight_only_linear(
+    x: torch.Tensor,
+    qweight: torch.Tensor,
+    scales: torch.Tensor,
+    bias: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """W8A16 linear ``y = x @ dequant(qweight, scales).T + bias``.
+
+    ``x``: ``[..., K]`` fp16/bf16; ``qweight``: int8 ``[N, K]``; ``scales``: fp32
+    ``[N]``; returns ``[..., N]`` in ``x.dtype``.
+    """
+    _check_w8a16(x, qweight, scales, bias)
+    K = x.shape[-1]
+    N = qweight.shape[0]
+    x_2d = x.contiguous().view(-1, K)
+    qweight = qweight.contiguous()
+    scales = scales.contiguous()
+    bias = None if bias is None else bias.contiguous()
+    M = x_2d.shape[0]
+    y = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    L = _lib.lib()
+    with torch.cuda.device(x.device):
+        ws_bytes = L.b200q_workspace_bytes(_lib.OP_W8A16, M, N, K)
+        ws = _workspace(x.device, ws_bytes)
+        rc = L.b200q_w8a16_gemm(x_2d.data_ptr(), qweight.data_ptr(), scales.data_ptr(),
+                                None if bias is None else bias.data_ptr(), y.data_ptr(), M, N, K,
+                                _DTYPE_IDS[x.dtype], None if ws is None else ws.data_ptr(),
+                                0 if ws is None else ws.numel(), _stream_ptr(x.device))
+    _lib.check(rc, "b200q_w8a16_gemm", f"M={M} N={N} K={K}")
+    return y.view(*x.shape[:-1], N)
+
+
+def _check_w8a8(x_q, a_scales, qweight, w_scales, bias, out_dtype) -> None:
+    _require_cuda(x_q, a_scales, qweight, w_scales)
+    ok = (x_q.dtype == torch.int8 and qweight.dtype == torch.int8
+          and a_scales.dtype == torch.float32 and w_scales.dtype == torch.float32
+          and out_dtype in _DTYPE_IDS and x_q.dim() == 2 and qweight.dim() == 2
+          and x_q.numel() > 0 and qweight.numel() > 0)
+    if not ok:
+        raise RuntimeError("CUDA W8A8 backend does not support the provided tensors")
+    if x_q.shape[-1] != qweight.shape[-1]:
+        raise RuntimeError(f"Incompatible shapes: x_q[-1]={x_q.shape[-1]} vs qweight[-1]={qweight.shape[-1]}")
+    if a_scales.dim() != 1 or a_scales.numel() != x_q.shape[0]:
+        raise RuntimeError("a_scales must be 1D with one value per input row")
+    if w_scales.dim() != 1 or w_scales.numel() != qweight.shape[0]:
+        raise RuntimeError("w_scales must be 1D with one value per output channel")
+    if bias is not None:
+        if bias.dim() != 1 or bias.numel() != qweight.shape[0]:
+            raise RuntimeError("bias must be 1D with one value per output channel")
+        if bias.dtype != out_dtype or not bias.is_cuda:
+            raise RuntimeError("bias must be a CUDA tensor of the output dtype")
+
+
+def apply_w8a8_linear(
+    x_q: torch.Tensor,
+    a_scales: torch.Tensor,
+    qweight: torch.Tensor,
+    w_scales: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    out_dtype: torch.dtype = torch.float16,
+    out_shape: tuple[int, ...] | None = None,
+) -> torch.Tensor:
+    """W8A8 linear: exact int32 ``x_q @ qweight.T``, then
+    ``(acc * a_scales[:, None]) * w_scales[None, :] + bias`` cast to ``out_dtype``."""
+    _check_w8a8(x_q, a_scales, qweight, w_scales, bias, out_dtype)
+    x_q = x_q.contiguous()
+    a_scales = a_scales.contiguous()
+    qweight = qweight.contiguous()
+    w_scales = w_scales.contiguous()
+    bias = None if bias is None else bias.contiguous()
+    M, K = x_q.shape
+    N = qweight.shape[0]
+    y = torch.empty((M, N), dtype=out_dtype, device=x_q.device)
+    L = _lib.lib()
+    with torch.cuda.device(x_q.device):
+        ws_bytes = L.b200q_workspace_bytes(_lib.OP_W8A8, M, N, K)
+        ws = _workspace(x_q.device, ws_bytes)
+        rc = L.b200q_w8a8_gemm(x_q.data_ptr(), a_scales.data_ptr(), qweight.data_ptr(),
+                               w_scales.data_ptr(), None if bias is None else bias.data_ptr(),
+                               y.data_ptr(), M, N, K, _DTYPE_IDS[out_dtype],
+                               None if ws is None else ws.data_ptr(),
+                               0 if ws is None else ws.numel(), _stream_ptr(x_q.device))
+    _lib.check(rc, "b200q_w8a8_gemm", f"M={M} N={N} K={K}")
+    return y if out_shape is None else y.view(out_shape)
+
+
+def w8a8_int32_accumulators(x_q: torch.Tensor, qweight: torch.Tensor) -> torch.Tensor:
+    """Raw int32 ``x_q @ qweight.T`` from the same kernels (parity/debug entry)."""
+    _require_cuda(x_q, qweight)
+    if x_q.dtype != torch.int8 or qweight.dtype != torch.int8 or x_q.dim() != 2 or qweight.dim() != 2:
+        raise RuntimeError("w8a8_int32_accumulators expects 2-D int8 tensors")
+    if x_q.shape[1] != qweight.shape[1]:
+        raise RuntimeError("x_q and qweight shapes do not align")
+    x_q = x_q.contiguous()
+    qweight = qweight.contiguous()
+    M, K = x_q.shape
+    N = qweight.shape[0]
+    acc = torch.empty((M, N), dtype=torch.int32, device=x_q.device)
+    L = _lib.lib()
+    with torch.cuda.device(x_q.device):
+        ws_bytes = L.b200q_workspace_bytes(_lib.OP_W8A8, M, N, K)
+        ws = _workspace(x_q.device, ws_bytes)
+        rc = L.b200q_w8a8_gemm_i32(x_q.data_ptr(), qweight.data_ptr(), acc.data_ptr(), M, N, K,
+                                   None if ws is None else ws.data_ptr(),
+                                   0 if ws is None else ws.numel(), _stream_ptr(x_q.device))
+    _lib.check(rc, "b200q_w8a8_gemm_i32", f"M={M} N={N} K={K}")
+    return acc

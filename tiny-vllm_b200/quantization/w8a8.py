@@ -1,0 +1,36 @@
+"""W8A8: int8 weights (fp32 scale per output channel) and per-token dynamically
+quantised int8 activations, int32 accumulation.
+
+Mirrors ``W8A8QuantMethod`` of the reference (``nanovllm/quantization/w8a8.py:9-40``):
+parameters ``qweight`` int8 ``[N, K]`` and ``w_scales`` fp32 ``[N]``; ``apply`` flattens
+the tokens, quantises them, and runs the int8 GEMM with the fused scale epilogue.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .base import QuantMethod, frozen
+from .cuda import apply_w8a8_linear, quantize_activation_int8
+
+
+class W8A8QuantMethod(QuantMethod):
+
+    def create_weights(self, layer: nn.Module, input_size: int, output_size: int) -> None:
+        layer.qweight = frozen((output_size, input_size), torch.int8)
+        layer.w_scales = frozen((output_size,), torch.float32)
+
+    def quantize_activation(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        tokens = x.reshape(-1, x.shape[-1])
+        return quantize_activation_int8(tokens)
+
+    def apply(self, x: torch.Tensor, layer: nn.Module,
+              bias: torch.Tensor | None = None) -> torch.Tensor:
+        x_q, a_scales = self.quantize_activation(x)
+        n_out = layer.qweight.shape[0]
+        return apply_w8a8_linear(
+            x_q, a_scales, layer.qweight, layer.w_scales,
+            bias=layer.bias if bias is None else bias,
+            out_dtype=x.dtype,
+            out_shape=(*x.shape[:-1], n_out),
+        )
