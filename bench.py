@@ -194,30 +194,30 @@ def run_gpu_arm(args):
     prev_dtype = torch.get_default_dtype()
     torch.set_default_dtype(torch.bfloat16)
     layers, work = [], []
-    with torch.device(dev):
-        for i, (name, K, N, split) in enumerate(PROJECTIONS):
-            q_full, s_full = O.make_weight(N, K, seed=i)
-            x_full = O.make_activation(TOKENS, K, seed=i)
+    for i, (name, K, N, split) in enumerate(PROJECTIONS):
+        q_full, s_full = O.make_weight(N, K, seed=i)
+        x_full = O.make_activation(TOKENS, K, seed=i)
+        with torch.device(dev):
             if name == "qkv":
                 layer = LL.QKVParallelLinear(K, 128, 16, 8, quantization="w8a8")
             elif name == "gate_up":
                 layer = LL.MergedColumnParallelLinear(K, [N // 2, N // 2], quantization="w8a8")
             else:
                 layer = LL.RowParallelLinear(K, N, quantization="w8a8")
-            layer.qweight.weight_loader(layer.qweight, q_full)
-            layer.w_scales.weight_loader(layer.w_scales, s_full)
-            x_local = x_full if split == "col" else x_full.chunk(tp, dim=1)[rank].contiguous()
-            layers.append(layer)
-            n_loc, k_loc = layer.qweight.shape
-            work.append({
-                "name": name, "split": split, "K": k_loc, "N": n_loc,
-                "x_host": x_local.pin_memory(), "x": x_local.to(dev),
-                "xq": torch.empty(TOKENS, k_loc, dtype=torch.int8, device=dev),
-                "a_s": torch.empty(TOKENS, dtype=torch.float32, device=dev),
-                "y": torch.empty(TOKENS, n_loc, dtype=torch.bfloat16, device=dev),
-                "y_host": torch.empty(TOKENS, n_loc, dtype=torch.bfloat16).pin_memory(),
-                "layer": layer, "ops": 2.0 * TOKENS * k_loc * n_loc,
-            })
+        layer.qweight.weight_loader(layer.qweight, q_full)
+        layer.w_scales.weight_loader(layer.w_scales, s_full)
+        x_local = x_full if split == "col" else x_full.chunk(tp, dim=1)[rank].contiguous()
+        layers.append(layer)
+        n_loc, k_loc = layer.qweight.shape
+        work.append({
+            "name": name, "split": split, "K": k_loc, "N": n_loc,
+            "x_host": x_local.pin_memory(), "x": x_local.to(dev),
+            "xq": torch.empty(TOKENS, k_loc, dtype=torch.int8, device=dev),
+            "a_s": torch.empty(TOKENS, dtype=torch.float32, device=dev),
+            "y": torch.empty(TOKENS, n_loc, dtype=torch.bfloat16, device=dev),
+            "y_host": torch.empty(TOKENS, n_loc, dtype=torch.bfloat16, device="cpu").pin_memory(),
+            "layer": layer, "ops": 2.0 * TOKENS * k_loc * n_loc,
+        })
     torch.set_default_dtype(prev_dtype)
     ws_bytes = max([L.b200q_workspace_bytes(_lib.OP_W8A8, TOKENS, w["N"], w["K"]) for w in work] + [16])
     ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)

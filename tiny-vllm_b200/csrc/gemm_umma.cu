@@ -35,8 +35,13 @@ namespace {
 constexpr int kTileA = 128;       // UMMA M
 constexpr int kBlockK = 128;      // bytes of K per pipeline stage = one swizzle row
 constexpr int kUmmaK = 32;        // bytes of K per tcgen05.mma kind::i8
-constexpr int kThreads = 192;     // 6 warps
-constexpr int kEpiThreads = 128;  // warps 2..5
+constexpr int kEpiWarps = 8;      // warps 2..9: two per TMEM lane quarter
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;  // + warp 0 (TMA) + warp 1 (UMMA)
+constexpr int kSlabBytes = 32 * 64;         // staging slab of the TMA-store epilogue: 32 rows x 32 cols x 2 B
+constexpr int kStagingBytes = kEpiWarps * 2 * kSlabBytes;
+constexpr int kScaleSmemBytes = 2 * 256 * 4;  // channel scales of the current tile, double-buffered
+constexpr int kCtrlBytes = 256;
 constexpr int kMaxStages = 8;
 constexpr int kMaxSmem = 227 * 1024;
 
@@ -59,6 +64,7 @@ struct KernelParams {
   int32_t* partials;
   unsigned int* counters;
   int* status;
+  int tma_store;           // 1: epilogue stages 16-bit tiles in shared memory and stores them with TMA
 };
 
 template <typename T>
@@ -114,7 +120,9 @@ __device__ __forceinline__ void emit_chunk(const KernelParams& p, int tile_a, in
         for (int j = 0; j < 32; j += 4)
           *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
       } else {
-        for (int j = 0; j < 32 && col_b0 + j < p.rows_b; ++j) dst[j] = static_cast<int32_t>(v[j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col_b0 + j < p.rows_b) dst[j] = static_cast<int32_t>(v[j]);
       }
     } else {
       const float a_s = __ldg(p.a_scales + row_a);
@@ -142,10 +150,13 @@ __device__ __forceinline__ void emit_chunk(const KernelParams& p, int tile_a, in
           *reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(dst) + j) =
               make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
       } else {
-        for (int j = 0; j < 32 && col_b0 + j < p.rows_b; ++j) {
-          const float b = bias != nullptr ? to_float<OutT>(bias[col_b0 + j]) : 0.f;
-          dst[j] = from_float<OutT>(
-              scale_acc(static_cast<int>(v[j]), a_s, __ldg(p.w_scales + col_b0 + j), b));
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (col_b0 + j < p.rows_b) {
+            const float b = bias != nullptr ? to_float<OutT>(bias[col_b0 + j]) : 0.f;
+            dst[j] = from_float<OutT>(
+                scale_acc(static_cast<int>(v[j]), a_s, __ldg(p.w_scales + col_b0 + j), b));
+          }
         }
       }
     }
@@ -176,16 +187,50 @@ __device__ __forceinline__ void emit_chunk(const KernelParams& p, int tile_a, in
   }
 }
 
+// 32 accumulators of one row -> 16-bit outputs, staged in a shared-memory slab
+// (32 rows x 64 bytes, 64-byte swizzle) that one lane then hands to a TMA store.
+template <typename OutT>
+__device__ __forceinline__ void stage_chunk(const KernelParams& p, const float* s_ws, float a_s,
+                                            int col0, int lane, uint8_t* slab,
+                                            const uint32_t (&v)[32]) {
+  const OutT* bias = reinterpret_cast<const OutT*>(p.bias);
+  uint32_t packed[16];
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 ws = *reinterpret_cast<const float4*>(s_ws + j);
+    float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+    if (bias != nullptr) {
+      if (col0 + j + 0 < p.rows_b) b0 = to_float<OutT>(bias[col0 + j + 0]);
+      if (col0 + j + 1 < p.rows_b) b1 = to_float<OutT>(bias[col0 + j + 1]);
+      if (col0 + j + 2 < p.rows_b) b2 = to_float<OutT>(bias[col0 + j + 2]);
+      if (col0 + j + 3 < p.rows_b) b3 = to_float<OutT>(bias[col0 + j + 3]);
+    }
+    packed[j / 2] = pack2<OutT>(scale_acc(static_cast<int>(v[j]), a_s, ws.x, b0),
+                                scale_acc(static_cast<int>(v[j + 1]), a_s, ws.y, b1));
+    packed[j / 2 + 1] = pack2<OutT>(scale_acc(static_cast<int>(v[j + 2]), a_s, ws.z, b2),
+                                    scale_acc(static_cast<int>(v[j + 3]), a_s, ws.w, b3));
+  }
+  // 64-byte swizzle: 16-byte chunk c of row r lives at chunk c ^ ((r >> 1) & 3)
+  const int sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    *reinterpret_cast<uint4*>(slab + lane * 64 + ((c ^ sw) << 4)) =
+        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+  }
+}
+
 template <typename OutT, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ CUtensorMap tmap_b, const KernelParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  // The swizzled operand tiles need 1024-byte alignment.
-  uint8_t* smem = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+                 const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_y, const KernelParams p) {
+  // Swizzled operand tiles need 1024-byte alignment; the dynamic shared window starts on
+  // such a boundary (checked below, the kernel refuses to run otherwise).
+  extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t stage_bytes = kTileA * kBlockK + p.bn * kBlockK;
-  uint8_t* ctrl = smem + static_cast<size_t>(p.stages) * stage_bytes;
+  uint8_t* staging = smem + static_cast<size_t>(p.stages) * stage_bytes;
+  float* s_ws = reinterpret_cast<float*>(staging + kStagingBytes);
+  uint8_t* ctrl = reinterpret_cast<uint8_t*>(s_ws) + kScaleSmemBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* tfull_bar = empty_bar + kMaxStages;
@@ -197,6 +242,10 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = ptx::smem_u32(smem);
+  if ((smem_base & 1023u) != 0u) {  // uniform over the CTA: nothing has been set up yet
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 0x200);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -213,6 +262,7 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::fence_mbar_init();
     ptx::tma_prefetch_desc(&tmap_a);
     ptx::tma_prefetch_desc(&tmap_b);
+    if (p.tma_store) ptx::tma_prefetch_desc(&tmap_y);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(tmem_slot), static_cast<uint32_t>(p.tmem_cols));
@@ -300,9 +350,16 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    // Warp (2 + e): TMEM lanes [32*(warp & 3), +32), 32-column chunks e/4, e/4 + 2, ...
+    const int epi_warp = warp - 2;
+    const int quarter = warp & 3;
+    const int half = epi_warp >> 2;
     const int row_in_tile = quarter * 32 + lane;
     const int epi_tid = threadIdx.x - 64;
+    const int n_chunks_tile = p.bn >> 5;
+    const int my_chunks = (n_chunks_tile - half + 1) >> 1;
+    uint8_t* my_slabs = staging + epi_warp * 2 * kSlabBytes;
+    uint32_t slab_turn = 0;
     int it = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
       const int split = item % p.splits;
@@ -311,33 +368,72 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int tile_b = t / p.tiles_a;
       const int buf = it & 1;
       const uint32_t tphase = static_cast<uint32_t>(it >> 1) & 1u;
+      float a_s = 0.f;
+      float* ws_tile = s_ws + buf * 256;
+      if (p.tma_store) {
+        // channel scales of this tile -> shared memory (while the main loop still runs)
+        const int col = tile_b * p.bn + epi_tid;
+        if (epi_tid < p.bn) ws_tile[epi_tid] = col < p.rows_b ? __ldg(p.w_scales + col) : 0.f;
+        const int row = tile_a * kTileA + row_in_tile;
+        if (row < p.rows_a) a_s = __ldg(p.a_scales + row);
+        ptx::named_bar_sync(2, kEpiThreads);
+      }
       if (!ptx::mbar_wait(ptx::smem_u32(tfull_bar + buf), tphase, abort_flag)) break;
       ptx::tc_fence_after_sync();
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * p.bn);
-      if (p.splits == 1) {
-        for (int c0 = 0; c0 < p.bn; c0 += 32) {
-          uint32_t v[32];
-          ptx::tmem_ld_32x32b_x32(taddr + c0, v);
-          ptx::tmem_ld_wait();
-          emit_chunk<OutT, MODE>(p, tile_a, tile_b, row_in_tile, c0, v);
-        }
-        ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(ptx::smem_u32(tempty_bar + buf));
-      } else {
-        // split-K: park the partial tile, the last CTA to arrive sums all of them.
-        int32_t* mine = p.partials +
-                        (static_cast<size_t>(t) * p.splits + split) * p.bn * kTileA + row_in_tile;
-        for (int c0 = 0; c0 < p.bn; c0 += 32) {
-          uint32_t v[32];
-          ptx::tmem_ld_32x32b_x32(taddr + c0, v);
-          ptx::tmem_ld_wait();
+      int32_t* mine = nullptr;
+      if (p.splits > 1)
+        mine = p.partials + (static_cast<size_t>(t) * p.splits + split) * p.bn * kTileA + row_in_tile;
+
+      // What happens to one 32-column chunk once it is in registers.
+      auto consume = [&](int c0, const uint32_t (&v)[32]) {
+        if (p.splits > 1) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             __stcg(mine + static_cast<size_t>(c0 + j) * kTileA, static_cast<int32_t>(v[j]));
+        } else if (p.tma_store) {
+          const int row0 = tile_a * kTileA + quarter * 32;
+          const int col0 = tile_b * p.bn + c0;
+          if (row0 < p.rows_a && col0 < p.rows_b) {  // warp-uniform
+            uint8_t* slab = my_slabs + (slab_turn & 1u) * kSlabBytes;
+            ++slab_turn;
+            // the store issued two chunks ago from this slab must have read it
+            if (lane == 0) ptx::bulk_wait_group_read<1>();
+            __syncwarp();
+            stage_chunk<OutT>(p, ws_tile + c0, a_s, col0, lane, slab, v);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d(&tmap_y, ptx::smem_u32(slab), col0, row0);
+              ptx::bulk_commit_group();
+            }
+          }
+        } else {
+          emit_chunk<OutT, MODE>(p, tile_a, tile_b, row_in_tile, c0, v);
         }
-        ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(ptx::smem_u32(tempty_bar + buf));
+      };
+
+      // Software-pipelined TMEM reads: the load of chunk k+1 is in flight while chunk k
+      // is converted and stored.
+      uint32_t va[32], vb[32];
+      if (my_chunks > 0) ptx::tmem_ld_32x32b_x32(taddr + half * 32, va);
+      for (int k = 0; k < my_chunks; k += 2) {
+        ptx::tmem_ld_wait();
+        if (k + 1 < my_chunks) ptx::tmem_ld_32x32b_x32(taddr + (half + 2 * (k + 1)) * 32, vb);
+        consume((half + 2 * k) * 32, va);
+        if (k + 1 < my_chunks) {
+          ptx::tmem_ld_wait();
+          if (k + 2 < my_chunks) ptx::tmem_ld_32x32b_x32(taddr + (half + 2 * (k + 2)) * 32, va);
+          consume((half + 2 * (k + 1)) * 32, vb);
+        }
+      }
+      // all TMEM reads of this thread are complete: hand the accumulator back
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(ptx::smem_u32(tempty_bar + buf));
+
+      if (p.splits > 1) {
+        // split-K: the last CTA to arrive for this tile sums all partial tiles.
         __threadfence();
         ptx::named_bar_sync(1, kEpiThreads);
         if (epi_tid == 0) {
@@ -351,7 +447,8 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
           __threadfence();
           const int32_t* base =
               p.partials + static_cast<size_t>(t) * p.splits * p.bn * kTileA + row_in_tile;
-          for (int c0 = 0; c0 < p.bn; c0 += 32) {
+          for (int k = 0; k < my_chunks; ++k) {
+            const int c0 = (half + 2 * k) * 32;
             uint32_t v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0u;
@@ -366,6 +463,8 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+    // shared-memory slabs must outlive the TMA stores that read them
+    if (p.tma_store && lane == 0) ptx::bulk_wait_group<0>();
   }
 
   // ---------------------------------------------------------------- teardown
@@ -402,33 +501,38 @@ EncodeTiledFn encode_fn() {
 
 struct MapKey {
   const void* base;
-  uint64_t rows, kbytes;
+  uint64_t rows, row_bytes;
   uint32_t box_rows;
+  int kind;  // 0: operand (bytes, 128-byte swizzle), 1: 16-bit output (64-byte swizzle)
   int device;
   bool operator==(const MapKey& o) const {
-    return base == o.base && rows == o.rows && kbytes == o.kbytes && box_rows == o.box_rows &&
-           device == o.device;
+    return base == o.base && rows == o.rows && row_bytes == o.row_bytes &&
+           box_rows == o.box_rows && kind == o.kind && device == o.device;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
     size_t h = reinterpret_cast<size_t>(k.base);
     h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
-    h ^= k.kbytes * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
-    h ^= (static_cast<size_t>(k.box_rows) << 8) ^ static_cast<size_t>(k.device);
+    h ^= k.row_bytes * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+    h ^= (static_cast<size_t>(k.box_rows) << 8) ^ static_cast<size_t>(k.device) ^
+         (static_cast<size_t>(k.kind) << 20);
     return h;
   }
 };
 
-// Descriptor of a dense row-major byte matrix [rows, kbytes], box = 128 bytes x box_rows,
-// 128-byte swizzle, zero fill outside the matrix.  Cached: encoding costs microseconds.
-bool get_tensor_map(const void* base, uint64_t rows, uint64_t kbytes, uint32_t box_rows,
-                    CUtensorMap* out) {
+// Tensor map of a dense row-major matrix, cached (encoding costs microseconds).
+//   kind 0: operand viewed as bytes [rows, row_bytes], box 128 bytes x box_rows, 128-byte
+//           swizzle, zero fill outside the matrix;
+//   kind 1: 16-bit output [rows, row_bytes / 2 elements], box 32 elements x 32 rows,
+//           64-byte swizzle (the layout the epilogue writes its staging slabs in).
+bool get_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                    int kind, CUtensorMap* out) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   int dev = 0;
   cudaGetDevice(&dev);
-  MapKey key{base, rows, kbytes, box_rows, dev};
+  MapKey key{base, rows, row_bytes, box_rows, kind, dev};
   {
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
@@ -439,14 +543,23 @@ bool get_tensor_map(const void* base, uint64_t rows, uint64_t kbytes, uint32_t b
   }
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
-  cuuint64_t dims[2] = {kbytes, rows};
-  cuuint64_t strides[1] = {kbytes};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), box_rows};
+  cuuint64_t strides[1] = {row_bytes};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
-  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r;
+  if (kind == 0) {
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), box_rows};
+    r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims[2] = {row_bytes / 2, rows};
+    cuuint32_t box[2] = {32, box_rows};
+    r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) {
     note_cuda_error(cudaErrorInvalidValue);
     return false;
@@ -469,8 +582,8 @@ int env_int(const char* name, int dflt) {
 }
 
 template <typename OutT, int MODE>
-cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp,
-                          const UmmaPlan& plan, cudaStream_t stream) {
+cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ty,
+                          const KernelParams& kp, const UmmaPlan& plan, cudaStream_t stream) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -480,7 +593,7 @@ cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const Ke
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  kern<<<plan.grid, kThreads, plan.smem_bytes, stream>>>(ta, tb, kp);
+  kern<<<plan.grid, kThreads, plan.smem_bytes, stream>>>(ta, tb, ty, kp);
   return cudaGetLastError();
 }
 
@@ -532,11 +645,12 @@ bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan) {
   pl.splits = (pl.k_blocks + pl.kb_per_split - 1) / pl.kb_per_split;
   if (pl.splits > 1 && tiles * sizeof(unsigned int) > kCounterBytes) return false;
   const int stage_bytes = kTileA * kBlockK + bn * kBlockK;
-  int stages = (kMaxSmem - 1024 - 256) / stage_bytes;
+  constexpr int kFixedSmem = kStagingBytes + kScaleSmemBytes + kCtrlBytes;
+  int stages = (kMaxSmem - kFixedSmem) / stage_bytes;
   stages = std::min(stages, kMaxStages);
   stages = std::min(stages, std::max(2, pl.kb_per_split * 2));
   pl.stages = stages;
-  pl.smem_bytes = static_cast<size_t>(stages) * stage_bytes + 1024 + 256;
+  pl.smem_bytes = static_cast<size_t>(stages) * stage_bytes + kFixedSmem;
   int cols = 32;
   while (cols < 2 * bn) cols *= 2;
   pl.tmem_cols = cols;
@@ -556,8 +670,13 @@ int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
   const void* base_a = plan.swap ? static_cast<const void*>(a.w) : a.x;
   const void* base_b = plan.swap ? a.x : static_cast<const void*>(a.w);
   CUtensorMap ta, tb;
-  if (!get_tensor_map(base_a, plan.rows_a, a.K, kTileA, &ta)) return B200Q_ERR_LAUNCH;
-  if (!get_tensor_map(base_b, plan.rows_b, a.K, plan.bn, &tb)) return B200Q_ERR_LAUNCH;
+  if (!get_tensor_map(base_a, plan.rows_a, a.K, kTileA, 0, &ta)) return B200Q_ERR_LAUNCH;
+  if (!get_tensor_map(base_b, plan.rows_b, a.K, plan.bn, 0, &tb)) return B200Q_ERR_LAUNCH;
+  // Prefill orientation, 16-bit output, no split-K: the epilogue stores through TMA.
+  const bool tma_store = !plan.swap && a.acc_out == nullptr && plan.splits == 1 && (a.N % 8) == 0;
+  CUtensorMap ty = ta;  // placeholder when unused
+  if (tma_store && !get_tensor_map(a.y, a.M, static_cast<uint64_t>(a.N) * 2, 32, 1, &ty))
+    return B200Q_ERR_LAUNCH;
 
   KernelParams kp{};
   kp.rows_a = plan.rows_a;
@@ -582,14 +701,15 @@ int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
                     ? reinterpret_cast<int32_t*>(static_cast<uint8_t*>(a.workspace) + kCounterBytes)
                     : nullptr;
   kp.status = a.status;
+  kp.tma_store = tma_store ? 1 : 0;
 
   cudaError_t e;
   if (a.acc_out != nullptr) {
-    e = launch_kernel<__nv_bfloat16, OUT_I32>(ta, tb, kp, plan, a.stream);
+    e = launch_kernel<__nv_bfloat16, OUT_I32>(ta, tb, ty, kp, plan, a.stream);
   } else if (a.dtype == B200Q_DTYPE_BF16) {
-    e = launch_kernel<__nv_bfloat16, OUT_SCALED>(ta, tb, kp, plan, a.stream);
+    e = launch_kernel<__nv_bfloat16, OUT_SCALED>(ta, tb, ty, kp, plan, a.stream);
   } else {
-    e = launch_kernel<__half, OUT_SCALED>(ta, tb, kp, plan, a.stream);
+    e = launch_kernel<__half, OUT_SCALED>(ta, tb, ty, kp, plan, a.stream);
   }
   if (e != cudaSuccess) {
     note_cuda_error(e);
