@@ -38,8 +38,8 @@ constexpr int kUmmaK = 32;        // bytes of K per tcgen05.mma kind::i8
 constexpr int kEpiWarps = 8;      // warps 2..9: two per TMEM lane quarter
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kThreads = 64 + kEpiThreads;  // + warp 0 (TMA) + warp 1 (UMMA)
-constexpr int kSlabBytes = 32 * 64;         // staging slab of the TMA-store epilogue: 32 rows x 32 cols x 2 B
-constexpr int kStagingBytes = kEpiWarps * 2 * kSlabBytes;
+constexpr int kSlabBytes = 32 * 128;         // per-warp transpose buffer: 32 rows x 64 cols x 2 B
+constexpr int kStagingBytes = kEpiWarps * kSlabBytes;
 constexpr int kScaleSmemBytes = 2 * 256 * 4;  // channel scales of the current tile, double-buffered
 constexpr int kCtrlBytes = 256;
 constexpr int kMaxStages = 8;
@@ -64,7 +64,8 @@ struct KernelParams {
   int32_t* partials;
   unsigned int* counters;
   int* status;
-  int tma_store;           // 1: epilogue stages 16-bit tiles in shared memory and stores them with TMA
+  int debug_flags;         // test-only: 1 = skip epilogue work, 2 = skip UMMA issue
+  int fast_store;          // 1: 16-bit outputs are transposed through shared memory and stored as full 128-byte rows
 };
 
 template <typename T>
@@ -187,43 +188,82 @@ __device__ __forceinline__ void emit_chunk(const KernelParams& p, int tile_a, in
   }
 }
 
-// 32 accumulators of one row -> 16-bit outputs, staged in a shared-memory slab
-// (32 rows x 64 bytes, 64-byte swizzle) that one lane then hands to a TMA store.
-template <typename OutT>
-__device__ __forceinline__ void stage_chunk(const KernelParams& p, const float* s_ws, float a_s,
-                                            int col0, int lane, uint8_t* slab,
-                                            const uint32_t (&v)[32]) {
+template <typename T>
+__device__ __forceinline__ uint32_t pack2_rn(float2 v);
+template <>
+__device__ __forceinline__ uint32_t pack2_rn<__nv_bfloat16>(float2 v) {
+  const __nv_bfloat162 h = __float22bfloat162_rn(v);  // one cvt.rn.bf16x2.f32
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2_rn<__half>(float2 v) {
+  const __half2 h = __float22half2_rn(v);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// 32 accumulators of one row -> 16 packed 16-bit pairs, written to this thread's row of
+// the warp's transpose buffer (rows of 128 bytes, 16-byte chunk c of row r stored at
+// chunk c ^ (r & 7) so that both the row-wise writes and the later reads are free of
+// bank conflicts).  Packed fp32x2 arithmetic (mul.f32x2 / add.f32x2 round each half like
+// the scalar instruction, so results are unchanged): (acc * a_s) * w_s [+ bias].
+template <typename OutT, bool HAS_BIAS>
+__device__ __forceinline__ void convert_chunk(const KernelParams& p, const float* s_ws, float a_s,
+                                              int col0, int lane, int chunk_half, uint8_t* slab,
+                                              const uint32_t (&v)[32]) {
   const OutT* bias = reinterpret_cast<const OutT*>(p.bias);
+  const float2 a2 = make_float2(a_s, a_s);
   uint32_t packed[16];
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
     const float4 ws = *reinterpret_cast<const float4*>(s_ws + j);
-    float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
-    if (bias != nullptr) {
-      if (col0 + j + 0 < p.rows_b) b0 = to_float<OutT>(bias[col0 + j + 0]);
-      if (col0 + j + 1 < p.rows_b) b1 = to_float<OutT>(bias[col0 + j + 1]);
-      if (col0 + j + 2 < p.rows_b) b2 = to_float<OutT>(bias[col0 + j + 2]);
-      if (col0 + j + 3 < p.rows_b) b3 = to_float<OutT>(bias[col0 + j + 3]);
+    float2 lo = make_float2(static_cast<float>(static_cast<int>(v[j])),
+                            static_cast<float>(static_cast<int>(v[j + 1])));
+    float2 hi = make_float2(static_cast<float>(static_cast<int>(v[j + 2])),
+                            static_cast<float>(static_cast<int>(v[j + 3])));
+    lo = __fmul2_rn(__fmul2_rn(lo, a2), make_float2(ws.x, ws.y));
+    hi = __fmul2_rn(__fmul2_rn(hi, a2), make_float2(ws.z, ws.w));
+    if (HAS_BIAS) {
+      float b[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        b[u] = col0 + j + u < p.rows_b ? to_float<OutT>(bias[col0 + j + u]) : 0.f;
+      lo = __fadd2_rn(lo, make_float2(b[0], b[1]));
+      hi = __fadd2_rn(hi, make_float2(b[2], b[3]));
     }
-    packed[j / 2] = pack2<OutT>(scale_acc(static_cast<int>(v[j]), a_s, ws.x, b0),
-                                scale_acc(static_cast<int>(v[j + 1]), a_s, ws.y, b1));
-    packed[j / 2 + 1] = pack2<OutT>(scale_acc(static_cast<int>(v[j + 2]), a_s, ws.z, b2),
-                                    scale_acc(static_cast<int>(v[j + 3]), a_s, ws.w, b3));
+    packed[j / 2] = pack2_rn<OutT>(lo);
+    packed[j / 2 + 1] = pack2_rn<OutT>(hi);
   }
-  // 64-byte swizzle: 16-byte chunk c of row r lives at chunk c ^ ((r >> 1) & 3)
-  const int sw = (lane >> 1) & 3;
+  const int sw = lane & 7;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    *reinterpret_cast<uint4*>(slab + lane * 64 + ((c ^ sw) << 4)) =
+    const int chunk = chunk_half * 4 + c;  // 16-byte chunk index inside the 128-byte row
+    *reinterpret_cast<uint4*>(slab + lane * 128 + ((chunk ^ sw) << 4)) =
         make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+  }
+}
+
+// Reads the warp's 32 x 64 transpose buffer back row-wise (8 lanes per 128-byte row) and
+// stores full rows: every store instruction writes four complete 128-byte lines.
+template <typename OutT>
+__device__ __forceinline__ void store_group(const KernelParams& p, const uint8_t* slab, int lane,
+                                            int row0, int col0) {
+  const int c = lane & 7;
+  const int col = col0 + c * 8;
+  OutT* out = reinterpret_cast<OutT*>(p.out);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    const uint4 val = *reinterpret_cast<const uint4*>(slab + r * 128 + ((c ^ (r & 7)) << 4));
+    const int row = row0 + r;
+    if (row < p.rows_a && col < p.rows_b)  // N % 8 == 0: a 16-byte piece is all in or all out
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * p.n_channels + col) = val;
   }
 }
 
 template <typename OutT, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_y, const KernelParams p) {
+                 const __grid_constant__ CUtensorMap tmap_b, const KernelParams p) {
   // Swizzled operand tiles need 1024-byte alignment; the dynamic shared window starts on
   // such a boundary (checked below, the kernel refuses to run otherwise).
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -262,7 +302,6 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::fence_mbar_init();
     ptx::tma_prefetch_desc(&tmap_a);
     ptx::tma_prefetch_desc(&tmap_b);
-    if (p.tma_store) ptx::tma_prefetch_desc(&tmap_y);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(tmem_slot), static_cast<uint32_t>(p.tmem_cols));
@@ -335,6 +374,7 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t b_desc = ptx::umma_desc_k_sw128(sb);
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            if (p.debug_flags & 2) break;
             // advancing K by 32 bytes inside the swizzled row = +2 in 16-byte units
             ptx::umma_i8_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
                             (kb > kb0 || k > 0) ? 1u : 0u);
@@ -350,16 +390,17 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    // Warp (2 + e): TMEM lanes [32*(warp & 3), +32), 32-column chunks e/4, e/4 + 2, ...
+    // Warp (2 + e) owns TMEM lanes [32*(warp & 3), +32) and the 64-column groups
+    // e/4, e/4 + 2, ... of the tile.
     const int epi_warp = warp - 2;
     const int quarter = warp & 3;
     const int half = epi_warp >> 2;
     const int row_in_tile = quarter * 32 + lane;
     const int epi_tid = threadIdx.x - 64;
-    const int n_chunks_tile = p.bn >> 5;
-    const int my_chunks = (n_chunks_tile - half + 1) >> 1;
-    uint8_t* my_slabs = staging + epi_warp * 2 * kSlabBytes;
-    uint32_t slab_turn = 0;
+    const int n_chunks_tile = p.bn >> 5;                 // 32-column chunks in the tile
+    const int n_groups_tile = (n_chunks_tile + 1) >> 1;  // 64-column groups (last may be half)
+    const int my_groups = (n_groups_tile - half + 1) >> 1;
+    uint8_t* slab = staging + epi_warp * kSlabBytes;
     int it = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
       const int split = item % p.splits;
@@ -368,9 +409,10 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int tile_b = t / p.tiles_a;
       const int buf = it & 1;
       const uint32_t tphase = static_cast<uint32_t>(it >> 1) & 1u;
+      const bool fast = p.fast_store && p.splits == 1;
       float a_s = 0.f;
       float* ws_tile = s_ws + buf * 256;
-      if (p.tma_store) {
+      if (fast && !(p.debug_flags & 8)) {
         // channel scales of this tile -> shared memory (while the main loop still runs)
         const int col = tile_b * p.bn + epi_tid;
         if (epi_tid < p.bn) ws_tile[epi_tid] = col < p.rows_b ? __ldg(p.w_scales + col) : 0.f;
@@ -386,46 +428,58 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (p.splits > 1)
         mine = p.partials + (static_cast<size_t>(t) * p.splits + split) * p.bn * kTileA + row_in_tile;
 
-      // What happens to one 32-column chunk once it is in registers.
+      // One 32-column chunk in registers -> its destination (generic paths).
       auto consume = [&](int c0, const uint32_t (&v)[32]) {
         if (p.splits > 1) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             __stcg(mine + static_cast<size_t>(c0 + j) * kTileA, static_cast<int32_t>(v[j]));
-        } else if (p.tma_store) {
-          const int row0 = tile_a * kTileA + quarter * 32;
-          const int col0 = tile_b * p.bn + c0;
-          if (row0 < p.rows_a && col0 < p.rows_b) {  // warp-uniform
-            uint8_t* slab = my_slabs + (slab_turn & 1u) * kSlabBytes;
-            ++slab_turn;
-            // the store issued two chunks ago from this slab must have read it
-            if (lane == 0) ptx::bulk_wait_group_read<1>();
-            __syncwarp();
-            stage_chunk<OutT>(p, ws_tile + c0, a_s, col0, lane, slab, v);
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              ptx::tma_store_2d(&tmap_y, ptx::smem_u32(slab), col0, row0);
-              ptx::bulk_commit_group();
-            }
-          }
         } else {
           emit_chunk<OutT, MODE>(p, tile_a, tile_b, row_in_tile, c0, v);
         }
       };
 
-      // Software-pipelined TMEM reads: the load of chunk k+1 is in flight while chunk k
-      // is converted and stored.
+      // Each group = two 32-column TMEM reads issued together.  The reads of group g+1 are
+      // issued as soon as the registers of group g have been converted, so they are in
+      // flight while group g is written out.
       uint32_t va[32], vb[32];
-      if (my_chunks > 0) ptx::tmem_ld_32x32b_x32(taddr + half * 32, va);
-      for (int k = 0; k < my_chunks; k += 2) {
+      if (p.debug_flags & 16) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) va[j] = vb[j] = j + lane;
+      }
+      auto issue = [&](int g) {
+        const int c = (half + 2 * g) * 2;  // first 32-column chunk of the group
+        if (p.debug_flags & 16) return;
+        ptx::tmem_ld_32x32b_x32(taddr + c * 32, va);
+        if (c + 1 < n_chunks_tile) ptx::tmem_ld_32x32b_x32(taddr + (c + 1) * 32, vb);
+      };
+      if (my_groups > 0) issue(0);
+      for (int g = 0; g < my_groups; ++g) {
+        const int c = (half + 2 * g) * 2;
+        const bool two = c + 1 < n_chunks_tile;
         ptx::tmem_ld_wait();
-        if (k + 1 < my_chunks) ptx::tmem_ld_32x32b_x32(taddr + (half + 2 * (k + 1)) * 32, vb);
-        consume((half + 2 * k) * 32, va);
-        if (k + 1 < my_chunks) {
-          ptx::tmem_ld_wait();
-          if (k + 2 < my_chunks) ptx::tmem_ld_32x32b_x32(taddr + (half + 2 * (k + 2)) * 32, va);
-          consume((half + 2 * (k + 1)) * 32, vb);
+        if (p.debug_flags & 1) {
+          if (g + 1 < my_groups) issue(g + 1);
+          continue;
+        }
+        if (fast) {
+          const int row0 = tile_a * kTileA + quarter * 32;
+          const int col0 = tile_b * p.bn + c * 32;
+          if (p.bias != nullptr) {
+            convert_chunk<OutT, true>(p, ws_tile + c * 32, a_s, col0, lane, 0, slab, va);
+            if (two) convert_chunk<OutT, true>(p, ws_tile + c * 32 + 32, a_s, col0 + 32, lane, 1, slab, vb);
+          } else {
+            convert_chunk<OutT, false>(p, ws_tile + c * 32, a_s, col0, lane, 0, slab, va);
+            if (two) convert_chunk<OutT, false>(p, ws_tile + c * 32 + 32, a_s, col0 + 32, lane, 1, slab, vb);
+          }
+          if (g + 1 < my_groups) issue(g + 1);
+          __syncwarp();
+          if (!(p.debug_flags & 4)) store_group<OutT>(p, slab, lane, row0, col0);
+          __syncwarp();
+        } else {
+          consume(c * 32, va);
+          if (two) consume(c * 32 + 32, vb);
+          if (g + 1 < my_groups) issue(g + 1);
         }
       }
       // all TMEM reads of this thread are complete: hand the accumulator back
@@ -447,8 +501,8 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
           __threadfence();
           const int32_t* base =
               p.partials + static_cast<size_t>(t) * p.splits * p.bn * kTileA + row_in_tile;
-          for (int k = 0; k < my_chunks; ++k) {
-            const int c0 = (half + 2 * k) * 32;
+          for (int ch = half; ch < n_chunks_tile; ch += 2) {
+            const int c0 = ch * 32;
             uint32_t v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0u;
@@ -463,8 +517,6 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-    // shared-memory slabs must outlive the TMA stores that read them
-    if (p.tma_store && lane == 0) ptx::bulk_wait_group<0>();
   }
 
   // ---------------------------------------------------------------- teardown
@@ -582,8 +634,8 @@ int env_int(const char* name, int dflt) {
 }
 
 template <typename OutT, int MODE>
-cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ty,
-                          const KernelParams& kp, const UmmaPlan& plan, cudaStream_t stream) {
+cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp,
+                          const UmmaPlan& plan, cudaStream_t stream) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -593,7 +645,7 @@ cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const CU
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  kern<<<plan.grid, kThreads, plan.smem_bytes, stream>>>(ta, tb, ty, kp);
+  kern<<<plan.grid, kThreads, plan.smem_bytes, stream>>>(ta, tb, kp);
   return cudaGetLastError();
 }
 
@@ -672,11 +724,10 @@ int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
   CUtensorMap ta, tb;
   if (!get_tensor_map(base_a, plan.rows_a, a.K, kTileA, 0, &ta)) return B200Q_ERR_LAUNCH;
   if (!get_tensor_map(base_b, plan.rows_b, a.K, plan.bn, 0, &tb)) return B200Q_ERR_LAUNCH;
-  // Prefill orientation, 16-bit output, no split-K: the epilogue stores through TMA.
-  const bool tma_store = !plan.swap && a.acc_out == nullptr && plan.splits == 1 && (a.N % 8) == 0;
-  CUtensorMap ty = ta;  // placeholder when unused
-  if (tma_store && !get_tensor_map(a.y, a.M, static_cast<uint64_t>(a.N) * 2, 32, 1, &ty))
-    return B200Q_ERR_LAUNCH;
+  // Prefill orientation, 16-bit output, no split-K: outputs are transposed through shared
+  // memory so that every store instruction writes complete 128-byte lines.
+  const bool fast_store = !plan.swap && a.acc_out == nullptr && plan.splits == 1 &&
+                          (a.N % 8) == 0 && (plan.bn % 64) == 0;
 
   KernelParams kp{};
   kp.rows_a = plan.rows_a;
@@ -701,15 +752,16 @@ int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
                     ? reinterpret_cast<int32_t*>(static_cast<uint8_t*>(a.workspace) + kCounterBytes)
                     : nullptr;
   kp.status = a.status;
-  kp.tma_store = tma_store ? 1 : 0;
+  kp.fast_store = fast_store ? 1 : 0;
+  kp.debug_flags = env_int("B200Q_DEBUG_FLAGS", 0);
 
   cudaError_t e;
   if (a.acc_out != nullptr) {
-    e = launch_kernel<__nv_bfloat16, OUT_I32>(ta, tb, ty, kp, plan, a.stream);
+    e = launch_kernel<__nv_bfloat16, OUT_I32>(ta, tb, kp, plan, a.stream);
   } else if (a.dtype == B200Q_DTYPE_BF16) {
-    e = launch_kernel<__nv_bfloat16, OUT_SCALED>(ta, tb, ty, kp, plan, a.stream);
+    e = launch_kernel<__nv_bfloat16, OUT_SCALED>(ta, tb, kp, plan, a.stream);
   } else {
-    e = launch_kernel<__half, OUT_SCALED>(ta, tb, ty, kp, plan, a.stream);
+    e = launch_kernel<__half, OUT_SCALED>(ta, tb, kp, plan, a.stream);
   }
   if (e != cudaSuccess) {
     note_cuda_error(e);
