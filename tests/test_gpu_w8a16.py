@@ -4,21 +4,24 @@ import pytest
 import torch
 
 from oracle import quant_linear_oracle as O
-from gpu_util import device_status_ok
+from gpu_util import device_status_ok, forced_path
 from tiny_vllm_b200.quantization.cuda import apply_int8_weight_only_linear
 
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("path", ["simt", "umma", "umma_swap", None])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,N,K,bias", [(1, 64, 128, False), (5, 96, 256, True), (37, 192, 256, True),
                                         (130, 320, 1024, False), (256, 6144, 1024, False),
-                                        (64, 1000, 1040, True)])
-def test_matches_reference_path(dtype, M, N, K, bias):
+                                        (64, 1000, 1040, True), (300, 512, 2048, True),
+                                        (513, 200, 48, False)])
+def test_matches_reference_path(path, dtype, M, N, K, bias):
     q, s = O.make_weight(N, K, seed=N)
     x = O.make_activation(M, K, seed=M, dtype=dtype, outliers=False)
     b = (torch.randn(N, generator=torch.Generator().manual_seed(1)) * 0.1).to(dtype) if bias else None
-    y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda())
+    with forced_path(path):
+        y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda())
     assert y.dtype == dtype and y.shape == (M, N)
     ref = O.w8a16_dequant_matmul(x, q, s, b)
     m = O.tensor_metrics(ref, y)
@@ -31,10 +34,47 @@ def test_matches_reference_path(dtype, M, N, K, bias):
 
 def test_golden_cases(golden_cases):
     for c in golden_cases:
-        y = apply_int8_weight_only_linear(c["x"].cuda(), c["q"].cuda(), c["s"].cuda(),
-                                          None if c["bias"] is None else c["bias"].cuda())
-        m = O.tensor_metrics(c["y_w8a16"], y)
-        assert m["relative_l2"] <= 1e-2 and m["cosine_similarity"] >= 0.9999, (c["id"], m)
+        for path in ("simt", "umma", "umma_swap"):
+            with forced_path(path):
+                y = apply_int8_weight_only_linear(c["x"].cuda(), c["q"].cuda(), c["s"].cuda(),
+                                                  None if c["bias"] is None else c["bias"].cuda())
+            m = O.tensor_metrics(c["y_w8a16"], y)
+            assert m["relative_l2"] <= 1e-2 and m["cosine_similarity"] >= 0.9999, (c["id"], path, m)
+
+
+def test_all_int8_codes_expand_exactly():
+    # every int8 value, -128 included, must reach the tensor cores unchanged: with x = identity
+    # rows and unit scales the output is the weight matrix itself
+    K = 256
+    q = torch.arange(-128, 128, dtype=torch.int16).to(torch.int8).repeat(128, 1)      # [128, 256]
+    q = torch.stack([torch.roll(q[i], i) for i in range(128)])
+    s = torch.ones(128)
+    for dtype in (torch.bfloat16, torch.float16):
+        x = torch.eye(K, dtype=dtype)
+        for path in ("umma", "umma_swap"):
+            with forced_path(path):
+                y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda())
+            assert torch.equal(y.float().cpu(), q.float().T), (dtype, path)
+
+
+@pytest.mark.parametrize("N,K", [(4096, 1024), (1024, 2048), (6144, 1024), (1024, 3072)])
+def test_baseline_prefill_shapes_full_size(N, K):
+    # M = 8192: sampled rows against the oracle, all rows through linearity in x
+    M = 8192
+    q, s = O.make_weight(N, K, seed=K)
+    x = O.make_activation(M, K, seed=K, outliers=False)
+    y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda())
+    rows = torch.arange(0, M, 331)
+    m = O.tensor_metrics(O.w8a16_dequant_matmul(x[rows], q, s), y[rows])
+    assert m["relative_l2"] <= 1e-2 and m["cosine_similarity"] >= 0.9999, m
+    m = O.tensor_metrics(O.w8a16_native_reference(x[rows], q, s), y[rows])
+    assert m["relative_l2"] <= 4e-3, m
+    # checksum over all rows: sum_n y[m, n] == x[m, :] @ (sum_n s[n] * q[n, :])
+    colsum = (q.double() * s.double()[:, None]).sum(dim=0)
+    expect = x.double() @ colsum
+    got = y.double().sum(dim=1).cpu()
+    assert torch.allclose(got, expect, rtol=2e-2, atol=2e-2 * float(expect.abs().mean()))
+    assert device_status_ok()
 
 
 def test_leading_dimensions_are_kept():

@@ -70,11 +70,19 @@ int auto_path_w8a8(int M, int N, int K) {
   return B200Q_PATH_UMMA;
 }
 
+// Kernel family for a W8A16 problem when nothing is forced.
+int auto_path_w8a16(int M, int N, int K) {
+  (void)N;
+  (void)K;
+  if (M <= 4) return B200Q_PATH_SIMT_STREAM;
+  if (M <= 256) return B200Q_PATH_UMMA_SWAP;
+  return B200Q_PATH_UMMA;
+}
+
 int resolve_path(int op, int M, int N, int K) {
   const int forced = g_forced_path.load();
-  if (op == B200Q_OP_W8A16) return B200Q_PATH_SIMT_STREAM;
   if (forced != B200Q_PATH_AUTO) return forced;
-  return auto_path_w8a8(M, N, K);
+  return op == B200Q_OP_W8A16 ? auto_path_w8a16(M, N, K) : auto_path_w8a8(M, N, K);
 }
 
 int run_w8a8(GemmArgs& a) {
@@ -216,22 +224,34 @@ int b200q_w8a16_gemm(const void* x, const int8_t* qweight, const float* scales, 
   a.workspace_bytes = workspace_bytes;
   a.status = d->status_ptr;
   a.stream = static_cast<cudaStream_t>(stream);
-  cudaError_t e = launch_w8a16_simt(a);
-  if (e != cudaSuccess) {
-    note_cuda_error(e);
-    return B200Q_ERR_LAUNCH;
+  const int path = resolve_path(B200Q_OP_W8A16, M, N, K);
+  if (path == B200Q_PATH_SIMT_STREAM) {
+    cudaError_t e = launch_w8a16_simt(a);
+    if (e != cudaSuccess) {
+      note_cuda_error(e);
+      return B200Q_ERR_LAUNCH;
+    }
+    return B200Q_OK;
   }
-  return B200Q_OK;
+  if (path == B200Q_PATH_UMMA || path == B200Q_PATH_UMMA_SWAP) {
+    UmmaPlan plan;
+    if (!umma16_make_plan(M, N, K, path == B200Q_PATH_UMMA_SWAP, &plan))
+      return B200Q_ERR_UNSUPPORTED_SHAPE;
+    return launch_w8a16_umma(a, plan);
+  }
+  return B200Q_ERR_BAD_ARGUMENT;
 }
 
 size_t b200q_workspace_bytes(int op, int M, int N, int K) {
-  if (op != B200Q_OP_W8A8) return 0;
+  if (op != B200Q_OP_W8A8 && op != B200Q_OP_W8A16) return 0;
   if (check_dims(M, N, K) != B200Q_OK) return 0;
   const int path = resolve_path(op, M, N, K);
   if (path != B200Q_PATH_UMMA && path != B200Q_PATH_UMMA_SWAP) return 0;
   UmmaPlan plan;
-  if (!umma_make_plan(op, M, N, K, path == B200Q_PATH_UMMA_SWAP, &plan)) return 0;
-  return plan.ws_bytes;
+  const bool ok = op == B200Q_OP_W8A8
+                      ? umma_make_plan(op, M, N, K, path == B200Q_PATH_UMMA_SWAP, &plan)
+                      : umma16_make_plan(M, N, K, path == B200Q_PATH_UMMA_SWAP, &plan);
+  return ok ? plan.ws_bytes : 0;
 }
 
 const char* b200q_select_path(int op, int M, int N, int K) {
@@ -239,14 +259,14 @@ const char* b200q_select_path(int op, int M, int N, int K) {
   if (op != B200Q_OP_W8A8 && op != B200Q_OP_W8A16) return "invalid_op";
   if (check_dims(M, N, K) != B200Q_OK) return "unsupported_shape";
   const int path = resolve_path(op, M, N, K);
-  if (op == B200Q_OP_W8A16) return "simt_stream_w8a16";
+  const bool a16 = op == B200Q_OP_W8A16;
   switch (path) {
     case B200Q_PATH_SIMT_STREAM:
-      return "simt_stream_dp4a";
+      return a16 ? "simt_stream_w8a16" : "simt_stream_dp4a";
     case B200Q_PATH_UMMA:
-      return "umma_i8_tokens128";
+      return a16 ? "umma_f16_expand_tokens128" : "umma_i8_tokens128";
     case B200Q_PATH_UMMA_SWAP:
-      return "umma_i8_channels128_splitk";
+      return a16 ? "umma_f16_expand_channels128_splitk" : "umma_i8_channels128_splitk";
     default:
       return "invalid_path";
   }

@@ -1,6 +1,7 @@
 // Internal declarations shared by the translation units of libb200q.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -61,6 +62,15 @@ cudaError_t launch_w8a16_simt(const GemmArgs& a);
 bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan);
 // Returns a B200Q_* code.
 int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan);
+
+// gemm_umma.cu: cached TMA descriptor of a dense row-major matrix viewed as bytes.
+bool get_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                    uint32_t box_bytes, CUtensorMap* out);
+int env_int(const char* name, int dflt);
+
+// gemm_umma_w8a16.cu
+bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan);
+int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan);
 
 void note_cuda_error(cudaError_t e);
 void count_launch(int n = 1);

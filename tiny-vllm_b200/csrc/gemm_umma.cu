@@ -554,12 +554,11 @@ EncodeTiledFn encode_fn() {
 struct MapKey {
   const void* base;
   uint64_t rows, row_bytes;
-  uint32_t box_rows;
-  int kind;  // 0: operand (bytes, 128-byte swizzle), 1: 16-bit output (64-byte swizzle)
+  uint32_t box_rows, box_bytes;
   int device;
   bool operator==(const MapKey& o) const {
     return base == o.base && rows == o.rows && row_bytes == o.row_bytes &&
-           box_rows == o.box_rows && kind == o.kind && device == o.device;
+           box_rows == o.box_rows && box_bytes == o.box_bytes && device == o.device;
   }
 };
 struct MapKeyHash {
@@ -568,23 +567,23 @@ struct MapKeyHash {
     h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
     h ^= k.row_bytes * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
     h ^= (static_cast<size_t>(k.box_rows) << 8) ^ static_cast<size_t>(k.device) ^
-         (static_cast<size_t>(k.kind) << 20);
+         (static_cast<size_t>(k.box_bytes) << 20);
     return h;
   }
 };
 
-// Tensor map of a dense row-major matrix, cached (encoding costs microseconds).
-//   kind 0: operand viewed as bytes [rows, row_bytes], box 128 bytes x box_rows, 128-byte
-//           swizzle, zero fill outside the matrix;
-//   kind 1: 16-bit output [rows, row_bytes / 2 elements], box 32 elements x 32 rows,
-//           64-byte swizzle (the layout the epilogue writes its staging slabs in).
+}  // namespace
+
+// Tensor map of a dense row-major matrix viewed as bytes [rows, row_bytes]: box =
+// box_bytes x box_rows with box_bytes = 128 (128-byte swizzle) or 64 (64-byte swizzle),
+// zero fill outside the matrix.  Cached: encoding costs microseconds.
 bool get_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
-                    int kind, CUtensorMap* out) {
+                    uint32_t box_bytes, CUtensorMap* out) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   int dev = 0;
   cudaGetDevice(&dev);
-  MapKey key{base, rows, row_bytes, box_rows, kind, dev};
+  MapKey key{base, rows, row_bytes, box_rows, box_bytes, dev};
   {
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
@@ -595,23 +594,15 @@ bool get_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_
   }
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {row_bytes, rows};
   cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {box_bytes, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
-  CUresult r;
-  if (kind == 0) {
-    cuuint64_t dims[2] = {row_bytes, rows};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), box_rows};
-    r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  } else {
-    cuuint64_t dims[2] = {row_bytes / 2, rows};
-    cuuint32_t box[2] = {32, box_rows};
-    r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
-           CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  }
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     note_cuda_error(cudaErrorInvalidValue);
     return false;
@@ -625,13 +616,15 @@ bool get_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_
   return true;
 }
 
-int round_up(int v, int m) { return (v + m - 1) / m * m; }
-
 int env_int(const char* name, int dflt) {
   const char* s = std::getenv(name);
   if (s == nullptr || *s == '\0') return dflt;
   return std::atoi(s);
 }
+
+namespace {
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 template <typename OutT, int MODE>
 cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp,
@@ -722,8 +715,8 @@ int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
   const void* base_a = plan.swap ? static_cast<const void*>(a.w) : a.x;
   const void* base_b = plan.swap ? a.x : static_cast<const void*>(a.w);
   CUtensorMap ta, tb;
-  if (!get_tensor_map(base_a, plan.rows_a, a.K, kTileA, 0, &ta)) return B200Q_ERR_LAUNCH;
-  if (!get_tensor_map(base_b, plan.rows_b, a.K, plan.bn, 0, &tb)) return B200Q_ERR_LAUNCH;
+  if (!get_tensor_map(base_a, plan.rows_a, a.K, kTileA, kBlockK, &ta)) return B200Q_ERR_LAUNCH;
+  if (!get_tensor_map(base_b, plan.rows_b, a.K, plan.bn, kBlockK, &tb)) return B200Q_ERR_LAUNCH;
   // Prefill orientation, 16-bit output, no split-K: outputs are transposed through shared
   // memory so that every store instruction writes complete 128-byte lines.
   const bool fast_store = !plan.swap && a.acc_out == nullptr && plan.splits == 1 &&

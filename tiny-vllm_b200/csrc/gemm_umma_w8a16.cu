@@ -1,0 +1,685 @@
+// W8A16 GEMM on the tcgen05 tensor cores: 16-bit activations x int8 weights.
+//
+//   y[m,n] = T( scales[n] * sum_k x[m,k] * float(q[n,k]) + bias[n] ),  fp32 accumulation
+//
+// The weights stay int8 in HBM and on their way into shared memory (TMA).  A group of
+// converter warps expands each int8 K block to the activation type (exact: |q| <= 128)
+// directly into the 128-byte-swizzled layout the UMMA descriptors expect, the tensor
+// cores run tcgen05.mma kind::f16 on the expanded tile, and the per-channel scale is
+// applied once in the fp32 epilogue.  The reference's fused kernel expands and scales
+// per product (nanovllm/quantization/csrc/int8_weight_only_gemm.cu:397-412,
+// 258-292); its Python path scales the whole matrix first (cuda.py:293-300); all three
+// compute the same sum up to rounding.
+//
+// Warp roles (320 threads, 1 CTA per SM, persistent):
+//   warp 0      TMA producer: 16-bit operand tile (128-byte swizzle) + raw int8 tile
+//               (64-byte swizzle) per K block of 64 elements
+//   warp 1      UMMA issuer (one thread): 4 x tcgen05.mma (K = 16) per K block
+//   warps 2-5   epilogue: tcgen05.ld -> acc * s[n] + b[n] -> 16 bit -> global
+//   warps 6-9   converters: raw int8 tile -> 16-bit swizzled tile (ring of 2 buffers)
+//
+// As in the W8A8 kernel the 128-row side of the UMMA tile holds the tokens for
+// prefill-sized problems and the output channels for decode-sized ones ("swap"), where K
+// is also split over CTAs; fp32 partial tiles are summed in a fixed order by the last CTA
+// to arrive, so results do not depend on scheduling.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+
+#include "common.h"
+#include "ptx_sm100.cuh"
+
+namespace b200q {
+namespace {
+
+constexpr int kTileA = 128;        // UMMA M
+constexpr int kBlockK = 64;        // K elements per pipeline stage
+constexpr int kRow16 = 128;        // bytes of one row of a 16-bit operand tile (= swizzle row)
+constexpr int kRow8 = 64;          // bytes of one row of the raw int8 tile
+constexpr int kUmmaK = 16;         // K elements per tcgen05.mma kind::f16
+constexpr int kEpiWarps = 4;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kConvWarps = 4;
+constexpr int kConvThreads = kConvWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads + kConvThreads;
+constexpr int kConvBufs = 2;
+constexpr int kMaxStages = 8;
+constexpr int kMaxSmem = 227 * 1024;
+constexpr int kSlabBytes = 32 * 128;  // per-epilogue-warp transpose buffer (32 rows x 64 cols x 2 B)
+constexpr int kStagingBytes = kEpiWarps * kSlabBytes;
+constexpr int kScaleSmemBytes = 2 * 256 * 4;
+constexpr int kCtrlBytes = 256;
+
+struct KernelParams {
+  int rows_a, rows_b;
+  int bn;
+  int tiles_a, tiles_b;
+  int k_blocks, splits, kb_per_split;
+  int stages;
+  int tmem_cols;
+  int swap;
+  int n_channels;
+  int is_bf16;
+  const float* w_scales;
+  const void* bias;
+  void* out;
+  float* partials;
+  unsigned int* counters;
+  int* status;
+  int fast_store;
+  int debug_flags;
+};
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) {
+  return __half2float(v);
+}
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack2_rn(float2 v);
+template <>
+__device__ __forceinline__ uint32_t pack2_rn<__nv_bfloat16>(float2 v) {
+  const __nv_bfloat162 h = __float22bfloat162_rn(v);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2_rn<__half>(float2 v) {
+  const __half2 h = __float22half2_rn(v);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// ------------------------------------------------------------ int8 -> 16-bit expansion
+// Four int8 (one 32-bit word) -> four values of type T, exact.
+//   fp16: 0x6400 | u is the half 1024 + u (u = q + 128 in 0..255); subtract 1152.
+//   bf16: 0x4B000000 | u is the float 2^23 + u; subtract 2^23 + 128; the result has at
+//         most 8 significant bits, so the conversion to bf16 is exact.
+template <typename T>
+__device__ __forceinline__ uint2 expand4(uint32_t w);
+template <>
+__device__ __forceinline__ uint2 expand4<__half>(uint32_t w) {
+  const uint32_t t = w ^ 0x80808080u;
+  uint32_t lo = __byte_perm(t, 0x64646464u, 0x4140);
+  uint32_t hi = __byte_perm(t, 0x64646464u, 0x4342);
+  const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+  const __half2 l = __hsub2(*reinterpret_cast<__half2*>(&lo), bias);
+  const __half2 h = __hsub2(*reinterpret_cast<__half2*>(&hi), bias);
+  return make_uint2(*reinterpret_cast<const uint32_t*>(&l), *reinterpret_cast<const uint32_t*>(&h));
+}
+template <>
+__device__ __forceinline__ uint2 expand4<__nv_bfloat16>(uint32_t w) {
+  const uint32_t t = w ^ 0x80808080u;
+  const float2 magic = make_float2(-8388736.f, -8388736.f);  // -(2^23 + 128)
+  const float2 f01 = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7540)),
+                                            __uint_as_float(__byte_perm(t, 0x4B000000u, 0x7541))),
+                                magic);
+  const float2 f23 = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7542)),
+                                            __uint_as_float(__byte_perm(t, 0x4B000000u, 0x7543))),
+                                magic);
+  return make_uint2(pack2_rn<__nv_bfloat16>(f01), pack2_rn<__nv_bfloat16>(f23));
+}
+
+// One row (64 int8) of the raw tile -> one row (128 bytes) of the 16-bit tile.
+//   raw tile : rows of 64 bytes, 64-byte swizzle  (chunk c of row r at c ^ ((r >> 1) & 3))
+//   16-bit   : rows of 128 bytes, 128-byte swizzle (chunk c of row r at c ^ (r & 7))
+template <typename T>
+__device__ __forceinline__ void expand_row(const uint8_t* raw, uint8_t* dst, int r) {
+  const uint8_t* src_row = raw + r * kRow8;
+  uint8_t* dst_row = dst + r * kRow16;
+  const int sw8 = (r >> 1) & 3;
+  const int sw16 = r & 7;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint4 w = *reinterpret_cast<const uint4*>(src_row + ((c ^ sw8) << 4));
+    const uint2 e0 = expand4<T>(w.x), e1 = expand4<T>(w.y), e2 = expand4<T>(w.z),
+                e3 = expand4<T>(w.w);
+    *reinterpret_cast<uint4*>(dst_row + (((2 * c) ^ sw16) << 4)) = make_uint4(e0.x, e0.y, e1.x, e1.y);
+    *reinterpret_cast<uint4*>(dst_row + (((2 * c + 1) ^ sw16) << 4)) =
+        make_uint4(e2.x, e2.y, e3.x, e3.y);
+  }
+}
+
+// ------------------------------------------------------------------------ epilogue
+__device__ __forceinline__ float scale_acc(float acc, float s, float b) {
+  return __fadd_rn(__fmul_rn(acc, s), b);
+}
+
+// Generic path: the 32 fp32 accumulators of columns [c0, c0+32) of this thread's row.
+template <typename OutT>
+__device__ __forceinline__ void emit_chunk(const KernelParams& p, int tile_a, int tile_b,
+                                           int row_in_tile, int c0, const uint32_t (&v)[32]) {
+  const int row_a = tile_a * kTileA + row_in_tile;
+  const int col_b0 = tile_b * p.bn + c0;
+  if (row_a >= p.rows_a || col_b0 >= p.rows_b) return;
+  const int N = p.n_channels;
+  const OutT* bias = reinterpret_cast<const OutT*>(p.bias);
+  OutT* out = reinterpret_cast<OutT*>(p.out);
+  if (!p.swap) {
+    OutT* dst = out + static_cast<size_t>(row_a) * N + col_b0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (col_b0 + j < p.rows_b) {
+        const float b = bias != nullptr ? to_float<OutT>(bias[col_b0 + j]) : 0.f;
+        dst[j] = from_float<OutT>(scale_acc(__uint_as_float(v[j]), __ldg(p.w_scales + col_b0 + j), b));
+      }
+    }
+  } else {
+    const float s = __ldg(p.w_scales + row_a);
+    const float b = bias != nullptr ? to_float<OutT>(bias[row_a]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int tok = col_b0 + j;
+      if (tok < p.rows_b)
+        out[static_cast<size_t>(tok) * N + row_a] = from_float<OutT>(scale_acc(__uint_as_float(v[j]), s, b));
+    }
+  }
+}
+
+// Fast path (tokens on rows): convert 32 accumulators and park them in this thread's
+// row of the warp's transpose buffer (rows of 128 bytes, 128-byte swizzle).
+template <typename OutT, bool HAS_BIAS>
+__device__ __forceinline__ void convert_chunk(const KernelParams& p, const float* s_ws, int col0,
+                                              int lane, int chunk_half, uint8_t* slab,
+                                              const uint32_t (&v)[32]) {
+  const OutT* bias = reinterpret_cast<const OutT*>(p.bias);
+  uint32_t packed[16];
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 ws = *reinterpret_cast<const float4*>(s_ws + j);
+    float2 lo = __fmul2_rn(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])),
+                           make_float2(ws.x, ws.y));
+    float2 hi = __fmul2_rn(make_float2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])),
+                           make_float2(ws.z, ws.w));
+    if (HAS_BIAS) {
+      float b[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        b[u] = col0 + j + u < p.rows_b ? to_float<OutT>(bias[col0 + j + u]) : 0.f;
+      lo = __fadd2_rn(lo, make_float2(b[0], b[1]));
+      hi = __fadd2_rn(hi, make_float2(b[2], b[3]));
+    }
+    packed[j / 2] = pack2_rn<OutT>(lo);
+    packed[j / 2 + 1] = pack2_rn<OutT>(hi);
+  }
+  const int sw = lane & 7;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int chunk = chunk_half * 4 + c;
+    *reinterpret_cast<uint4*>(slab + lane * 128 + ((chunk ^ sw) << 4)) =
+        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_group(const KernelParams& p, const uint8_t* slab, int lane,
+                                            int row0, int col0) {
+  const int c = lane & 7;
+  const int col = col0 + c * 8;
+  OutT* out = reinterpret_cast<OutT*>(p.out);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    const uint4 val = *reinterpret_cast<const uint4*>(slab + r * 128 + ((c ^ (r & 7)) << 4));
+    const int row = row0 + r;
+    if (row < p.rows_a && col < p.rows_b)
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * p.n_channels + col) = val;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                  const __grid_constant__ CUtensorMap tmap_w, const KernelParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  // rows of the 16-bit (activation) tile and of the int8 (weight) tile in one stage
+  const int rows16 = p.swap ? p.bn : kTileA;
+  const int rows8 = p.swap ? kTileA : p.bn;
+  const uint32_t tile16_bytes = rows16 * kRow16;
+  const uint32_t raw_bytes = rows8 * kRow8;
+  const uint32_t stage_bytes = tile16_bytes + raw_bytes;
+  const uint32_t conv_bytes = rows8 * kRow16;
+  uint8_t* conv_base = smem + static_cast<size_t>(p.stages) * stage_bytes;
+  uint8_t* staging = conv_base + kConvBufs * conv_bytes;
+  float* s_ws = reinterpret_cast<float*>(staging + kStagingBytes);
+  uint8_t* ctrl = reinterpret_cast<uint8_t*>(s_ws) + kScaleSmemBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* cfull_bar = empty_bar + kMaxStages;     // [kConvBufs] converted tile ready
+  uint64_t* cempty_bar = cfull_bar + kConvBufs;     // [kConvBufs] converted tile consumed
+  uint64_t* tfull_bar = cempty_bar + kConvBufs;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  if ((smem_base & 1023u) != 0u) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 0x200);
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(full_bar + s), 1);
+      ptx::mbar_init(ptx::smem_u32(empty_bar + s), 1);
+    }
+    for (int c = 0; c < kConvBufs; ++c) {
+      ptx::mbar_init(ptx::smem_u32(cfull_bar + c), kConvWarps);
+      ptx::mbar_init(ptx::smem_u32(cempty_bar + c), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(ptx::smem_u32(tfull_bar + b), 1);
+      ptx::mbar_init(ptx::smem_u32(tempty_bar + b), kEpiThreads);
+    }
+    *abort_flag = 0;
+    last_flag[0] = 0;
+    last_flag[1] = 0;
+    ptx::fence_mbar_init();
+    ptx::tma_prefetch_desc(&tmap_x);
+    ptx::tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), static_cast<uint32_t>(p.tmem_cols));
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_items = p.tiles_a * p.tiles_b * p.splits;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------ TMA producer
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const int split = item % p.splits;
+        const int t = item / p.splits;
+        const int tile_a = t % p.tiles_a;
+        const int tile_b = t / p.tiles_a;
+        // token tile / channel tile indices
+        const int row16 = p.swap ? tile_b * p.bn : tile_a * kTileA;
+        const int row8 = p.swap ? tile_a * kTileA : tile_b * p.bn;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(empty_bar + stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = ptx::smem_u32(full_bar + stage);
+          const uint32_t s16 = smem_base + stage * stage_bytes;
+          const uint32_t s8 = s16 + tile16_bytes;
+          ptx::mbar_arrive_expect_tx(bar, stage_bytes);
+          ptx::tma_load_2d(s16, &tmap_x, bar, kb * kBlockK * 2, row16);  // byte coordinate
+          ptx::tma_load_2d(s8, &tmap_w, bar, kb * kBlockK, row8);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------- UMMA issuer
+      const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+      const uint32_t idesc = ptx::umma_idesc(1u, fmt, kTileA, static_cast<uint32_t>(p.bn));
+      int stage = 0, cb = 0;
+      uint32_t phase = 0, cphase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++it) {
+        const int split = item % p.splits;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        const int buf = it & 1;
+        const uint32_t tphase = static_cast<uint32_t>(it >> 1) & 1u;
+        if (!ptx::mbar_wait(ptx::smem_u32(tempty_bar + buf), tphase ^ 1u, abort_flag)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.bn);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(full_bar + stage), phase, abort_flag) ||
+              !ptx::mbar_wait(ptx::smem_u32(cfull_bar + cb), cphase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t s16 = smem_base + stage * stage_bytes;
+          const uint32_t sconv = ptx::smem_u32(conv_base) + cb * conv_bytes;
+          const uint64_t d16 = ptx::umma_desc_k_sw128(s16);
+          const uint64_t dcv = ptx::umma_desc_k_sw128(sconv);
+          const uint64_t a_desc = p.swap ? dcv : d16;
+          const uint64_t b_desc = p.swap ? d16 : dcv;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // 16 elements of 2 bytes = 32 bytes along K = +2 in 16-byte units
+            ptx::umma_f16_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                             (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          ptx::umma_commit(ptx::smem_u32(empty_bar + stage));
+          ptx::umma_commit(ptx::smem_u32(cempty_bar + cb));
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+          if (++cb == kConvBufs) {
+            cb = 0;
+            cphase ^= 1u;
+          }
+        }
+        if (ok) ptx::umma_commit(ptx::smem_u32(tfull_bar + buf));
+      }
+    }
+  } else if (warp >= 2 + kEpiWarps) {
+    // ---------------------------------------------------------- converters
+    const int ctid = threadIdx.x - (64 + kEpiThreads);
+    int stage = 0, cb = 0;
+    uint32_t phase = 0, cphase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      const int split = item % p.splits;
+      const int kb0 = split * p.kb_per_split;
+      const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!ptx::mbar_wait(ptx::smem_u32(full_bar + stage), phase, abort_flag) ||
+            !ptx::mbar_wait(ptx::smem_u32(cempty_bar + cb), cphase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        const uint8_t* raw = smem + stage * stage_bytes + tile16_bytes;
+        uint8_t* dst = conv_base + cb * conv_bytes;
+        for (int r = ctid; r < rows8; r += kConvThreads) expand_row<T>(raw, dst, r);
+        ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the UMMA reads
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(cfull_bar + cb));
+        if (++stage == p.stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (++cb == kConvBufs) {
+          cb = 0;
+          cphase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int epi_warp = warp - 2;
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;
+    const int n_chunks_tile = p.bn >> 5;
+    const int n_groups = (n_chunks_tile + 1) >> 1;
+    uint8_t* slab = staging + epi_warp * kSlabBytes;
+    int it = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
+      const int split = item % p.splits;
+      const int t = item / p.splits;
+      const int tile_a = t % p.tiles_a;
+      const int tile_b = t / p.tiles_a;
+      const int buf = it & 1;
+      const uint32_t tphase = static_cast<uint32_t>(it >> 1) & 1u;
+      const bool fast = p.fast_store && p.splits == 1;
+      float* ws_tile = s_ws + buf * 256;
+      if (fast) {
+        for (int i = epi_tid; i < p.bn; i += kEpiThreads) {
+          const int col = tile_b * p.bn + i;
+          ws_tile[i] = col < p.rows_b ? __ldg(p.w_scales + col) : 0.f;
+        }
+        ptx::named_bar_sync(2, kEpiThreads);
+      }
+      if (!ptx::mbar_wait(ptx::smem_u32(tfull_bar + buf), tphase, abort_flag)) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr =
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * p.bn);
+      float* mine = nullptr;
+      if (p.splits > 1)
+        mine = p.partials + (static_cast<size_t>(t) * p.splits + split) * p.bn * kTileA + row_in_tile;
+
+      auto consume = [&](int c0, const uint32_t (&v)[32]) {
+        if (p.splits > 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            __stcg(mine + static_cast<size_t>(c0 + j) * kTileA, __uint_as_float(v[j]));
+        } else {
+          emit_chunk<T>(p, tile_a, tile_b, row_in_tile, c0, v);
+        }
+      };
+
+      uint32_t va[32], vb[32];
+      auto issue = [&](int g) {
+        const int c = 2 * g;
+        ptx::tmem_ld_32x32b_x32(taddr + c * 32, va);
+        if (c + 1 < n_chunks_tile) ptx::tmem_ld_32x32b_x32(taddr + (c + 1) * 32, vb);
+      };
+      issue(0);
+      for (int g = 0; g < n_groups; ++g) {
+        const int c = 2 * g;
+        const bool two = c + 1 < n_chunks_tile;
+        ptx::tmem_ld_wait();
+        if (fast) {
+          const int row0 = tile_a * kTileA + quarter * 32;
+          const int col0 = tile_b * p.bn + c * 32;
+          if (p.bias != nullptr) {
+            convert_chunk<T, true>(p, ws_tile + c * 32, col0, lane, 0, slab, va);
+            if (two) convert_chunk<T, true>(p, ws_tile + c * 32 + 32, col0 + 32, lane, 1, slab, vb);
+          } else {
+            convert_chunk<T, false>(p, ws_tile + c * 32, col0, lane, 0, slab, va);
+            if (two) convert_chunk<T, false>(p, ws_tile + c * 32 + 32, col0 + 32, lane, 1, slab, vb);
+          }
+          if (g + 1 < n_groups) issue(g + 1);
+          __syncwarp();
+          store_group<T>(p, slab, lane, row0, col0);
+          __syncwarp();
+        } else {
+          consume(c * 32, va);
+          if (two) consume(c * 32 + 32, vb);
+          if (g + 1 < n_groups) issue(g + 1);
+        }
+      }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(ptx::smem_u32(tempty_bar + buf));
+
+      if (p.splits > 1) {
+        __threadfence();
+        ptx::named_bar_sync(1, kEpiThreads);
+        if (epi_tid == 0) {
+          const unsigned int old = atomicAdd(p.counters + t, 1u);
+          const int last = (old == static_cast<unsigned int>(p.splits - 1));
+          if (last) p.counters[t] = 0u;
+          last_flag[it & 1] = last;
+        }
+        ptx::named_bar_sync(1, kEpiThreads);
+        if (last_flag[it & 1]) {
+          __threadfence();
+          const float* base =
+              p.partials + static_cast<size_t>(t) * p.splits * p.bn * kTileA + row_in_tile;
+          for (int ch = 0; ch < n_chunks_tile; ++ch) {
+            const int c0 = ch * 32;
+            uint32_t v[32];
+            float acc[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+            for (int s = 0; s < p.splits; ++s) {  // fixed order: deterministic sums
+              const float* src = base + static_cast<size_t>(s) * p.bn * kTileA;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                acc[j] = __fadd_rn(acc[j], __ldcg(src + static_cast<size_t>(c0 + j) * kTileA));
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(acc[j]);
+            emit_chunk<T>(p, tile_a, tile_b, row_in_tile, c0, v);
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0) {
+    atomicCAS(p.status, 0, 0x300 | (static_cast<int>(blockIdx.x) << 12));
+  }
+}
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+template <typename T>
+cudaError_t launch_kernel(const CUtensorMap& tx, const CUtensorMap& tw, const KernelParams& kp,
+                          const UmmaPlan& plan, cudaStream_t stream) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = w8a16_umma_kernel<T>;
+  if (dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  kern<<<plan.grid, kThreads, plan.smem_bytes, stream>>>(tx, tw, kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 16) != 0) return false;
+  UmmaPlan pl{};
+  pl.swap = swap;
+  pl.rows_a = swap ? N : M;
+  pl.rows_b = swap ? M : N;
+  const int sms = sm_count();
+  pl.k_blocks = (K + kBlockK - 1) / kBlockK;
+  int bn = pl.rows_b >= 256 ? 256 : round_up(pl.rows_b, 32);
+  if (!swap && pl.rows_b >= 256) {
+    const int ta = (pl.rows_a + kTileA - 1) / kTileA;
+    double best = 1e30;
+    for (int cand : {256, 128}) {
+      const int tiles = ta * ((pl.rows_b + cand - 1) / cand);
+      const int waves = (tiles + sms - 1) / sms;
+      const double cost = waves * (cand + 32.0);
+      if (cost < best) {
+        best = cost;
+        bn = cand;
+      }
+    }
+  }
+  bn = env_int("B200Q_DEBUG_BN", bn);
+  if (bn < 32 || bn > 256 || (bn % 32) != 0) return false;
+  pl.bn = bn;
+  pl.tiles_a = (pl.rows_a + kTileA - 1) / kTileA;
+  pl.tiles_b = (pl.rows_b + bn - 1) / bn;
+  const long long tiles = static_cast<long long>(pl.tiles_a) * pl.tiles_b;
+  if (tiles > 1 << 22) return false;
+  int splits = 1;
+  if (tiles < sms) {
+    splits = static_cast<int>(sms / tiles);
+    splits = std::min(splits, std::max(1, pl.k_blocks / 4));
+    splits = std::min(splits, 16);
+  }
+  splits = env_int("B200Q_DEBUG_SPLITS", splits);
+  if (splits < 1) splits = 1;
+  if (splits > pl.k_blocks) splits = pl.k_blocks;
+  pl.kb_per_split = (pl.k_blocks + splits - 1) / splits;
+  pl.splits = (pl.k_blocks + pl.kb_per_split - 1) / pl.kb_per_split;
+  if (pl.splits > 1 && tiles * sizeof(unsigned int) > kCounterBytes) return false;
+  const int rows16 = swap ? bn : kTileA;
+  const int rows8 = swap ? kTileA : bn;
+  const int stage_bytes = rows16 * kRow16 + rows8 * kRow8;
+  const int fixed = kConvBufs * rows8 * kRow16 + kStagingBytes + kScaleSmemBytes + kCtrlBytes;
+  int stages = (kMaxSmem - fixed) / stage_bytes;
+  stages = std::min(stages, kMaxStages);
+  stages = std::min(stages, std::max(2, pl.kb_per_split));
+  if (stages < 2) return false;
+  pl.stages = stages;
+  pl.smem_bytes = static_cast<size_t>(stages) * stage_bytes + fixed;
+  int cols = 32;
+  while (cols < 2 * bn) cols *= 2;
+  pl.tmem_cols = cols;
+  const long long items = tiles * pl.splits;
+  pl.grid = static_cast<int>(std::min<long long>(items, sms));
+  pl.ws_bytes = pl.splits > 1
+                    ? kCounterBytes + static_cast<size_t>(tiles) * pl.splits * bn * kTileA * sizeof(float)
+                    : 0;
+  *plan = pl;
+  return true;
+}
+
+int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan) {
+  if (plan.ws_bytes > 0) {
+    if (a.workspace == nullptr || a.workspace_bytes < plan.ws_bytes) return B200Q_ERR_WORKSPACE;
+  }
+  const int rows16 = plan.swap ? plan.bn : kTileA;
+  const int rows8 = plan.swap ? kTileA : plan.bn;
+  CUtensorMap tx, tw;
+  // activations: [M, 2K bytes], 128-byte boxes; weights: [N, K bytes], 64-byte boxes
+  if (!get_tensor_map(a.x, a.M, static_cast<uint64_t>(a.K) * 2, rows16, kRow16, &tx))
+    return B200Q_ERR_LAUNCH;
+  if (!get_tensor_map(a.w, a.N, a.K, rows8, kRow8, &tw)) return B200Q_ERR_LAUNCH;
+
+  KernelParams kp{};
+  kp.rows_a = plan.rows_a;
+  kp.rows_b = plan.rows_b;
+  kp.bn = plan.bn;
+  kp.tiles_a = plan.tiles_a;
+  kp.tiles_b = plan.tiles_b;
+  kp.k_blocks = plan.k_blocks;
+  kp.splits = plan.splits;
+  kp.kb_per_split = plan.kb_per_split;
+  kp.stages = plan.stages;
+  kp.tmem_cols = plan.tmem_cols;
+  kp.swap = plan.swap;
+  kp.n_channels = a.N;
+  kp.is_bf16 = a.dtype == B200Q_DTYPE_BF16 ? 1 : 0;
+  kp.w_scales = a.w_scales;
+  kp.bias = a.bias;
+  kp.out = a.y;
+  kp.counters = reinterpret_cast<unsigned int*>(a.workspace);
+  kp.partials = plan.ws_bytes > 0
+                    ? reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + kCounterBytes)
+                    : nullptr;
+  kp.status = a.status;
+  kp.fast_store = (!plan.swap && plan.splits == 1 && (a.N % 8) == 0 && (plan.bn % 64) == 0) ? 1 : 0;
+  kp.debug_flags = env_int("B200Q_DEBUG_FLAGS", 0);
+
+  cudaError_t e = a.dtype == B200Q_DTYPE_BF16
+                      ? launch_kernel<__nv_bfloat16>(tx, tw, kp, plan, a.stream)
+                      : launch_kernel<__half>(tx, tw, kp, plan, a.stream);
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  count_launch();
+  return B200Q_OK;
+}
+
+}  // namespace b200q
