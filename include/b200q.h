@@ -44,8 +44,12 @@ enum {
   B200Q_ERR_UNSUPPORTED_ARCH = 6,  /* current device is not compute capability 10.x */
   B200Q_ERR_LAUNCH = 7,            /* a CUDA runtime/driver call failed (see b200q_last_cuda_error) */
   B200Q_ERR_BAD_ARGUMENT = 8,      /* unknown op / dtype / path id */
-  B200Q_ERR_DEVICE_TIMEOUT = 9     /* a bounded device-side wait gave up (b200q_device_status) */
+  B200Q_ERR_DEVICE_TIMEOUT = 9,    /* a bounded device-side wait gave up (b200q_device_status) */
+  B200Q_ERR_SCRATCH_LIMIT = 10     /* problem needs more built-in scratch than B200Q_NOALLOC_SCRATCH_BYTES */
 };
+
+/* Size of the scratch area built into the library for b200q_w8a8_gemm_noalloc. */
+#define B200Q_NOALLOC_SCRATCH_BYTES (8u << 20)
 
 /* ---- element types of the floating-point side -------------------------- */
 enum {
@@ -159,6 +163,36 @@ int b200q_debug_force_path(int path);
 
 /* Test hook: number of kernels this library has launched in this process. */
 uint64_t b200q_launch_count(void);
+
+/*
+ * W8A8 linear for callers that have no way to hand over scratch memory.
+ * (No counterpart in the reference: its kernels never need scratch.)
+ *
+ * Same inputs, outputs and arithmetic as b200q_w8a8_gemm, but without the workspace
+ * arguments.  The decode-sized (split-K) kernel needs a few megabytes of scratch for its
+ * partial tiles and tile counters; b200q_w8a8_gemm takes that from the caller, who usually
+ * gets it from an allocator.  Two kinds of caller cannot do that: an embedder that binds
+ * this C ABI directly and owns no device allocator, and a serving process that has already
+ * given all remaining HBM to its KV cache after warm-up, where a late cudaMalloc would
+ * fail or would have to be carved out of the cache.  For them the scratch lives inside
+ * the library, in one fixed device array of B200Q_NOALLOC_SCRATCH_BYTES (8 MiB) that every
+ * GPU which loads the library holds until the process exits.
+ *
+ *  - Nothing is allocated or freed by this call, ever (no cudaMalloc / cudaFree).
+ *  - A problem whose split-K scratch would exceed the built-in array is refused with
+ *    B200Q_ERR_SCRATCH_LIMIT and nothing is launched; use b200q_w8a8_gemm with a
+ *    caller-owned workspace for it.  Problems that need no scratch are never refused.
+ *  - The first call on each device looks up the device address of the array (a one-time
+ *    host-side query with that device current).  Make that first call during start-up,
+ *    before any stream capture is begun.
+ *  - All calls share the one array, and the array keeps whatever the last call left in it;
+ *    the part that must start at zero (the tile counters) is cleared on the stream at
+ *    the start of every call.  Two calls that overlap on the GPU (different streams) race
+ *    on the array: keep calls on one device ordered on one stream.
+ */
+int b200q_w8a8_gemm_noalloc(const int8_t* xq, const float* a_scales, const int8_t* qweight,
+                            const float* w_scales, const void* bias, void* y, int M, int N,
+                            int K, int out_dtype, void* stream);
 
 #ifdef __cplusplus
 }

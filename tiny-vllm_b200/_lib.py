@@ -24,6 +24,8 @@ ERR_UNSUPPORTED_ARCH = 6
 ERR_LAUNCH = 7
 ERR_BAD_ARGUMENT = 8
 ERR_DEVICE_TIMEOUT = 9
+ERR_SCRATCH_LIMIT = 10
+NOALLOC_SCRATCH_BYTES = 8 << 20
 
 DTYPE_F16 = 0
 DTYPE_BF16 = 1
@@ -58,6 +60,9 @@ SIGNATURES = {
     "b200q_version": (_c.c_int, []),
     "b200q_debug_force_path": (_c.c_int, [_c.c_int]),
     "b200q_launch_count": (_c.c_uint64, []),
+    "b200q_w8a8_gemm_noalloc": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                           _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
+                                           _c.c_int, _c.c_void_p]),
 }
 
 _lock = threading.Lock()

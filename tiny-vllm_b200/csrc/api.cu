@@ -115,6 +115,16 @@ int sm_count() {
   return d != nullptr && d->sms > 0 ? d->sms : 148;
 }
 
+int device_cc_major() {
+  DeviceInfo* d = device_info();
+  return d != nullptr ? d->cc_major : 0;
+}
+
+int* device_status_ptr() {
+  DeviceInfo* d = device_info();
+  return d != nullptr ? d->status_ptr : nullptr;
+}
+
 void note_cuda_error(cudaError_t e) { g_last_cuda_error.store(static_cast<int>(e)); }
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n)); }
 
@@ -294,6 +304,9 @@ const char* b200q_strerror(int code) {
       return "unknown op, dtype or path id";
     case B200Q_ERR_DEVICE_TIMEOUT:
       return "a bounded device-side wait gave up";
+    case B200Q_ERR_SCRATCH_LIMIT:
+      return "problem needs more scratch than the library's built-in 8 MiB array; "
+             "use b200q_w8a8_gemm with a caller-owned workspace";
     default:
       return "unknown error code";
   }

@@ -49,6 +49,10 @@ constexpr size_t kCounterBytes = 16384;  // zero-initialised tile counters at wo
 
 // Number of SMs of the current device (cached).
 int sm_count();
+// Compute-capability major of the current device (0 on error) and the device address of
+// its status word (nullptr on error); both cached per device.
+int device_cc_major();
+int* device_status_ptr();
 
 // act_quant.cu
 cudaError_t launch_act_quant(const void* x, int64_t ldx, int x_dtype, int8_t* xq, float* a_scales,

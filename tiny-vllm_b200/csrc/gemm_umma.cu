@@ -764,4 +764,100 @@ int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
   return B200Q_OK;
 }
 
+// ------------------------------------------------------------ built-in scratch variant
+// Scratch for b200q_w8a8_gemm_noalloc: tile counters first, split-K partial tiles after
+// them.  Lives in every GPU context that loads the library, for the life of the process.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[B200Q_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+
+// Device address of g_noalloc_scratch on the current device.  In host code the array's
+// name is only a handle for the runtime, not an address a kernel could use, so the real
+// address is asked for once per device (with that device current) and remembered.
+unsigned char* noalloc_scratch_ptr() {
+  static std::mutex mu;
+  static unsigned char* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> g(mu);
+  if (cached[dev] == nullptr) {
+    unsigned char* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      note_cuda_error(e == cudaSuccess ? cudaErrorUnknown : e);
+      return nullptr;
+    }
+    cached[dev] = ptr;
+  }
+  return cached[dev];
+}
+
+}  // namespace
+
 }  // namespace b200q
+
+extern "C" int b200q_w8a8_gemm_noalloc(const int8_t* xq, const float* a_scales,
+                                       const int8_t* qweight, const float* w_scales,
+                                       const void* bias, void* y, int M, int N, int K,
+                                       int out_dtype, void* stream) {
+  using namespace b200q;
+  // Cheap argument checks first: same rules as b200q_w8a8_gemm.
+  if (xq == nullptr || a_scales == nullptr || qweight == nullptr || w_scales == nullptr ||
+      y == nullptr)
+    return B200Q_ERR_NULL_POINTER;
+  if (M <= 0 || N <= 0 || K <= 0 || static_cast<long long>(M) * N > 0x7FFFFFFFLL ||
+      static_cast<long long>(M) * K > 0x7FFFFFFFLL || static_cast<long long>(N) * K > 0x7FFFFFFFLL)
+    return B200Q_ERR_BAD_SHAPE;
+  if ((K % 16) != 0) return B200Q_ERR_UNSUPPORTED_SHAPE;
+  if (out_dtype != B200Q_DTYPE_F16 && out_dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  auto misaligned = [](const void* p, uintptr_t mask) {
+    return (reinterpret_cast<uintptr_t>(p) & mask) != 0;
+  };
+  if (misaligned(xq, 15) || misaligned(qweight, 15) || misaligned(y, 15) ||
+      misaligned(w_scales, 15) || misaligned(a_scales, 3) || (bias != nullptr && misaligned(bias, 1)))
+    return B200Q_ERR_MISALIGNED;
+  const int cc = device_cc_major();
+  if (cc == 0) return B200Q_ERR_LAUNCH;
+  if (cc != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+
+  // Decode-sized token counts take the split-K kernel (channels on the 128-row side),
+  // larger ones the prefill orientation, which needs no scratch for most shapes.
+  UmmaPlan plan;
+  if (!umma_make_plan(B200Q_OP_W8A8, M, N, K, M <= 256 ? 1 : 0, &plan))
+    return B200Q_ERR_UNSUPPORTED_SHAPE;
+  if (plan.ws_bytes > B200Q_NOALLOC_SCRATCH_BYTES) return B200Q_ERR_SCRATCH_LIMIT;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned char* scratch = nullptr;
+  if (plan.ws_bytes > 0) {
+    scratch = noalloc_scratch_ptr();  // first call on a device: one-time address look-up
+    if (scratch == nullptr) return B200Q_ERR_LAUNCH;
+    // The array still holds the previous call's data.  Only the tile counters have to
+    // start at zero; the partial tiles are fully overwritten before they are read.
+    const size_t counter_bytes =
+        static_cast<size_t>(plan.tiles_a) * plan.tiles_b * sizeof(unsigned int);
+    cudaError_t e = cudaMemsetAsync(scratch, 0, counter_bytes, st);
+    if (e != cudaSuccess) {
+      note_cuda_error(e);
+      return B200Q_ERR_LAUNCH;
+    }
+  }
+  GemmArgs a{};
+  a.x = xq;
+  a.w = qweight;
+  a.a_scales = a_scales;
+  a.w_scales = w_scales;
+  a.bias = bias;
+  a.y = y;
+  a.acc_out = nullptr;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.dtype = out_dtype;
+  a.workspace = scratch;
+  a.workspace_bytes = plan.ws_bytes > 0 ? B200Q_NOALLOC_SCRATCH_BYTES : 0;
+  a.status = device_status_ptr();
+  a.stream = st;
+  if (a.status == nullptr) return B200Q_ERR_LAUNCH;
+  return launch_w8a8_umma(a, plan);
+}
