@@ -38,21 +38,56 @@ __device__ __forceinline__ float absmax4(float m, const float2 a, const float2 b
   return fmaxf(fmaxf(m, fmaxf(fabsf(a.x), fabsf(a.y))), fmaxf(fabsf(b.x), fabsf(b.y)));
 }
 
-__device__ __forceinline__ uint32_t quant1(float v, float scale) {
+// Exact path for one element: clamp(rint(v / scale), -127, 127) as a byte (IEEE division).
+__device__ __forceinline__ uint32_t quant1_exact(float v, float scale) {
   int q = __float2int_rn(__fdiv_rn(v, scale));  // round half to even
   q = max(-127, min(127, q));
   return static_cast<uint32_t>(q) & 0xFFu;
 }
 
 template <typename T>
-__device__ __forceinline__ uint2 quant8(const uint4 raw, float scale) {
+__device__ __noinline__ uint2 quant8_exact(const uint4 raw, float scale) {
   const float2 a = unpack2<T>(raw.x), b = unpack2<T>(raw.y), c = unpack2<T>(raw.z),
                d = unpack2<T>(raw.w);
   uint2 o;
-  o.x = quant1(a.x, scale) | (quant1(a.y, scale) << 8) | (quant1(b.x, scale) << 16) |
-        (quant1(b.y, scale) << 24);
-  o.y = quant1(c.x, scale) | (quant1(c.y, scale) << 8) | (quant1(d.x, scale) << 16) |
-        (quant1(d.y, scale) << 24);
+  o.x = quant1_exact(a.x, scale) | (quant1_exact(a.y, scale) << 8) |
+        (quant1_exact(b.x, scale) << 16) | (quant1_exact(b.y, scale) << 24);
+  o.y = quant1_exact(c.x, scale) | (quant1_exact(c.y, scale) << 8) |
+        (quant1_exact(d.x, scale) << 16) | (quant1_exact(d.y, scale) << 24);
+  return o;
+}
+
+// Eight elements -> eight int8 codes, bit-identical to the IEEE division.
+// Fast path: t = v * (1/scale) is within 2 ulp of the true quotient (|t| <= 127, so within
+// 1.6e-5), hence rint(t) can differ from rint(v / scale) only when t lies that close to a
+// rounding tie k + 0.5.  A chunk that has such an element (|t - rint(t)| > 0.4999, about
+// one chunk in 600 for random data) is redone with exact divisions.  Rounding uses the
+// 1.5 * 2^23 trick: adding the constant rounds half-to-even to an integer and leaves that
+// integer in the low mantissa bits (two's complement), i.e. the low byte is the int8 code.
+// |t| cannot exceed 127 (1 + 2^-22) because scale >= absmax / 127, so no clamp is needed.
+// Packed fp32x2 instructions round each half like the scalar ones.
+template <typename T>
+__device__ __forceinline__ uint2 quant8(const uint4 raw, float scale, float inv_scale) {
+  const float2 inv2 = make_float2(inv_scale, inv_scale);
+  const float2 magic = make_float2(12582912.0f, 12582912.0f);      // 1.5 * 2^23
+  const float2 neg_magic = make_float2(-12582912.0f, -12582912.0f);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t ub[8];
+  float worst = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __fmul2_rn(unpack2<T>(w[i]), inv2);
+    const float2 u = __fadd2_rn(t, magic);
+    const float2 r = __fadd2_rn(u, neg_magic);
+    const float2 d = __fadd2_rn(t, make_float2(-r.x, -r.y));
+    worst = fmaxf(worst, fmaxf(fabsf(d.x), fabsf(d.y)));
+    ub[2 * i] = __float_as_uint(u.x);
+    ub[2 * i + 1] = __float_as_uint(u.y);
+  }
+  if (!(worst <= 0.4999f)) return quant8_exact<T>(raw, scale);  // also taken for NaN
+  uint2 o;
+  o.x = __byte_perm(__byte_perm(ub[0], ub[1], 0x0040), __byte_perm(ub[2], ub[3], 0x0040), 0x5410);
+  o.y = __byte_perm(__byte_perm(ub[4], ub[5], 0x0040), __byte_perm(ub[6], ub[7], 0x0040), 0x5410);
   return o;
 }
 
@@ -62,7 +97,7 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// G threads per row (32 or 256), CHUNKS 16-byte chunks per thread held in registers.
+// G threads per row (32, 64, 128 or 256), CHUNKS 16-byte chunks per thread held in registers.
 // Requires K <= G * 8 * CHUNKS.
 template <typename T, int G, int CHUNKS>
 __global__ void __launch_bounds__(256)
@@ -93,21 +128,24 @@ act_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__
   }
   amax = warp_max(amax);
   if (G > 32) {
+    // the row's G/32 warps are neighbours in the block: combine their maxima
+    constexpr int kWarpsPerRow = G / 32;
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
     __syncthreads();
-    float m = red[0];
+    float m = red[g * kWarpsPerRow];
 #pragma unroll
-    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+    for (int i = 1; i < kWarpsPerRow; ++i) m = fmaxf(m, red[g * kWarpsPerRow + i]);
     amax = m;
   }
   if (!active) return;
   const float scale = fmaxf(__fdiv_rn(amax, 127.0f), 1e-8f);
+  const float inv_scale = __frcp_rn(scale);
   if (t == 0) a_scales[row] = scale;
   uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<size_t>(row) * K);
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c) {
     const int idx = c * G + t;
-    if (idx < nchunk) dst[idx] = quant8<T>(raw[c], scale);
+    if (idx < nchunk) dst[idx] = quant8<T>(raw[c], scale, inv_scale);
   }
 }
 
@@ -133,26 +171,31 @@ act_quant_long_rows_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restr
 #pragma unroll
   for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
   const float scale = fmaxf(__fdiv_rn(m, 127.0f), 1e-8f);
+  const float inv_scale = __frcp_rn(scale);
   if (threadIdx.x == 0) a_scales[row] = scale;
   uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<size_t>(row) * K);
   for (int idx = threadIdx.x; idx < nchunk; idx += 256)
-    dst[idx] = quant8<T>(__ldg(src + idx), scale);
+    dst[idx] = quant8<T>(__ldg(src + idx), scale, inv_scale);
 }
 
 template <typename T>
 cudaError_t launch_typed(const T* x, int64_t ldx, int8_t* xq, float* a_scales, int M, int K,
                          cudaStream_t s) {
-  const int warp_rows_grid = (M + 7) / 8;  // 8 warps (rows) per 256-thread block
+  // Four 16-byte chunks per thread keep the register count low (high occupancy); longer
+  // rows are spread over more threads instead of more chunks.
+  auto blocks = [&](int g) { return (M + (256 / g) - 1) / (256 / g); };
   if (K <= 32 * 8 * 2) {
-    act_quant_rows_kernel<T, 32, 2><<<warp_rows_grid, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+    act_quant_rows_kernel<T, 32, 2><<<blocks(32), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
   } else if (K <= 32 * 8 * 4) {
-    act_quant_rows_kernel<T, 32, 4><<<warp_rows_grid, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
-  } else if (K <= 32 * 8 * 8) {
-    act_quant_rows_kernel<T, 32, 8><<<warp_rows_grid, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
-  } else if (K <= 32 * 8 * 16) {
-    act_quant_rows_kernel<T, 32, 16><<<warp_rows_grid, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+    act_quant_rows_kernel<T, 32, 4><<<blocks(32), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+  } else if (K <= 64 * 8 * 4) {
+    act_quant_rows_kernel<T, 64, 4><<<blocks(64), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+  } else if (K <= 128 * 8 * 4) {
+    act_quant_rows_kernel<T, 128, 4><<<blocks(128), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+  } else if (K <= 256 * 8 * 4) {
+    act_quant_rows_kernel<T, 256, 4><<<blocks(256), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
   } else if (K <= 256 * 8 * 8) {
-    act_quant_rows_kernel<T, 256, 8><<<M, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+    act_quant_rows_kernel<T, 256, 8><<<blocks(256), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
   } else {
     act_quant_long_rows_kernel<T><<<M, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
   }

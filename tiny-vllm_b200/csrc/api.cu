@@ -265,7 +265,7 @@ size_t b200q_workspace_bytes(int op, int M, int N, int K) {
 }
 
 const char* b200q_select_path(int op, int M, int N, int K) {
-  if (op == B200Q_OP_ACT_QUANT) return K <= 4096 ? "act_quant_warp_per_row" : "act_quant_cta_per_row";
+  if (op == B200Q_OP_ACT_QUANT) return K <= 1024 ? "act_quant_warp_per_row" : "act_quant_multiwarp_row";
   if (op != B200Q_OP_W8A8 && op != B200Q_OP_W8A16) return "invalid_op";
   if (check_dims(M, N, K) != B200Q_OK) return "unsupported_shape";
   const int path = resolve_path(op, M, N, K);
