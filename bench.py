@@ -78,8 +78,19 @@ def cpu_sweep_seconds(tokens: int, repeats: int):
     return best
 
 
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1; the CPU legs are meant to use every host core."""
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        pass
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
 def cpu_baseline(budget_s: float = 20.0):
-    threads = torch.get_num_threads()
+    threads = use_all_host_threads()
     probe_tokens = 256
     t_probe = cpu_sweep_seconds(probe_tokens, 1)
     per_token = t_probe / probe_tokens
@@ -97,7 +108,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    threads = torch.get_num_threads()
+    threads = use_all_host_threads()
     t_probe = cpu_sweep_seconds(256, 1)
     tokens = int(min(TOKENS, max(256, 1.5 / (t_probe / 256))))  # about 1.5 s per step at most
     tokens = max(256, tokens // 256 * 256)
@@ -301,8 +312,13 @@ def run_gpu_arm(args):
     peaks = load_peaks()
     int8_peak = 2.0 * peaks["bf16_sustained"]
     achieved = gemm_ops_total / (gemm_ms_total * 1e-3) / 1e12
+    # DRAM bytes per launch from the ncu capture summarised in
+    # profiles/w8a8_umma_kernel_prefill_sweep_m8192.md (mean of the four shapes, TP=1 only)
+    traffic = 130.2e6 / 4 if world == 1 else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
-                "frac": achieved / int8_peak, "traffic": None,
+                "frac": achieved / int8_peak, "traffic": traffic,
+                "traffic_note": "dram__bytes_read+write per launch, mean over the 4 shapes; algorithmic "
+                                "mean is 66.6 MB, the difference is output still dirty in L2 at kernel end",
                 "kernel": "w8a8_umma_kernel (tcgen05 kind::i8)",
                 "peak_note": f"2 x {peaks['source']} sustained bf16 dense TFLOP/s ({peaks['bf16_sustained']}); "
                              "int8 is the double-rate kind; nominal 4500"}

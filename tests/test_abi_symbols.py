@@ -73,7 +73,8 @@ def test_argument_validation_needs_no_device(L):
 
 
 def test_path_names_and_workspace_queries(L):
-    assert L.b200q_select_path(_lib.OP_W8A8, 8192, 4096, 1024) == b"umma_i8_tokens128"
+    assert L.b200q_select_path(_lib.OP_W8A8, 8192, 4096, 1024) == b"umma_i8_pair_tokens256"
+    assert L.b200q_select_path(_lib.OP_W8A8, 300, 4096, 1024) == b"umma_i8_tokens128"
     assert L.b200q_select_path(_lib.OP_W8A8, 16, 4096, 1024) == b"umma_i8_channels128_splitk"
     assert L.b200q_select_path(_lib.OP_W8A8, 1, 4096, 1024) == b"simt_stream_dp4a"
     assert L.b200q_select_path(_lib.OP_W8A8, 16, 4096, 1000) == b"unsupported_shape"

@@ -12,7 +12,7 @@ from oracle import quant_linear_oracle as O
 from gpu_util import bits, device_status_ok, forced_path
 from tiny_vllm_b200 import _lib
 from tiny_vllm_b200.quantization.cuda import (apply_w8a8_linear, quantize_activation_int8,
-                                              w8a8_int32_accumulators)
+                                              select_path, w8a8_int32_accumulators)
 
 pytestmark = pytest.mark.gpu
 
@@ -115,6 +115,21 @@ def test_baseline_prefill_shapes_full_size(N, K, oracle_c_lib):
     ref = O.w8a8_dequant_matmul(xq[rows], a_s[rows], q, s, None, torch.bfloat16)
     m = O.tensor_metrics(ref, y[rows])
     assert m["relative_l2"] <= REL_L2_GATE and m["cosine_similarity"] >= COSINE_GATE
+    assert device_status_ok()
+
+
+@pytest.mark.parametrize("M,N,K,dtype,bias", [(2500, 2056, 272, torch.bfloat16, True),
+                                              (2305, 2304, 1024, torch.float16, False),
+                                              (9000, 520, 128, torch.bfloat16, False)])
+def test_cta_pair_kernel_ragged_edges(M, N, K, dtype, bias, oracle_c_lib):
+    # shapes the CTA-pair (cta_group::2) kernel takes, with M not a multiple of 256 (the second
+    # CTA of the last pair is partly or wholly out of range), N not a multiple of 256 and a K tail
+    assert select_path(_lib.OP_W8A8, M, N, K) == "umma_i8_pair_tokens256"
+    x, xq, a_s, q, s, b = problem(M, N, K, seed=M, dtype=dtype, bias=bias)
+    y = apply_w8a8_linear(xq.cuda(), a_s.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda(),
+                          out_dtype=dtype)
+    expect = O.w8a8_native_epilogue(O.w8a8_int32_accumulators(xq, q), a_s, s, b, dtype)
+    assert torch.equal(bits(y.cpu()), bits(expect))
     assert device_status_ok()
 
 

@@ -99,6 +99,8 @@ int run_w8a8(GemmArgs& a) {
     }
     return B200Q_OK;
   }
+  if (path == B200Q_PATH_UMMA && umma_pair_applicable(a.M, a.N, a.K, a.acc_out != nullptr))
+    return launch_w8a8_umma_pair(a);
   if (path == B200Q_PATH_UMMA || path == B200Q_PATH_UMMA_SWAP) {
     UmmaPlan plan;
     if (!umma_make_plan(B200Q_OP_W8A8, a.M, a.N, a.K, path == B200Q_PATH_UMMA_SWAP, &plan))
@@ -274,6 +276,7 @@ const char* b200q_select_path(int op, int M, int N, int K) {
     case B200Q_PATH_SIMT_STREAM:
       return a16 ? "simt_stream_w8a16" : "simt_stream_dp4a";
     case B200Q_PATH_UMMA:
+      if (!a16 && umma_pair_applicable(M, N, K, false)) return "umma_i8_pair_tokens256";
       return a16 ? "umma_f16_expand_tokens128" : "umma_i8_tokens128";
     case B200Q_PATH_UMMA_SWAP:
       return a16 ? "umma_f16_expand_channels128_splitk" : "umma_i8_channels128_splitk";

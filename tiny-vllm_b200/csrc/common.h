@@ -72,6 +72,10 @@ bool get_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_
                     uint32_t box_bytes, CUtensorMap* out);
 int env_int(const char* name, int dflt);
 
+// gemm_umma_pair.cu: CTA-pair (cta_group::2) variant for prefill-sized W8A8 problems
+bool umma_pair_applicable(int M, int N, int K, bool raw_int32_out);
+int launch_w8a8_umma_pair(const GemmArgs& a);
+
 // gemm_umma_w8a16.cu
 bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan);
 int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan);

@@ -212,8 +212,10 @@ __device__ __forceinline__ void convert_chunk(const KernelParams& p, const float
 #pragma unroll
       for (int u = 0; u < 4; ++u)
         b[u] = col0 + j + u < p.rows_b ? to_float<OutT>(bias[col0 + j + u]) : 0.f;
-      lo = __fadd2_rn(lo, make_float2(b[0], b[1]));
-      hi = __fadd2_rn(hi, make_float2(b[2], b[3]));
+      // scalar adds: __fadd_rn is never contracted with the multiply before it (the
+      // packed add was seen fused into an fma.f32x2, one rounding instead of two)
+      lo = make_float2(__fadd_rn(lo.x, b[0]), __fadd_rn(lo.y, b[1]));
+      hi = make_float2(__fadd_rn(hi.x, b[2]), __fadd_rn(hi.y, b[3]));
     }
     packed[j / 2] = pack2_rn<OutT>(lo);
     packed[j / 2 + 1] = pack2_rn<OutT>(hi);
