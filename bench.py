@@ -252,11 +252,27 @@ def run_gpu_arm(args):
             if w["split"] == "row" and tp > 1:
                 dist.all_reduce(w["y"])
 
+    # End-to-end step: pinned host activations -> device -> layer API -> pinned host outputs.
+    # Uploads, compute and downloads run on three streams so that the two copy engines and
+    # the SMs work at the same time; the step ends when every output is back on the host.
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    s_main = torch.cuda.current_stream(dev)
+
     def e2e_step():
         for w in work:
-            x = w["x_host"].to(dev, non_blocking=True)
+            with torch.cuda.stream(s_in):
+                x = w["x_host"].to(dev, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            s_main.wait_event(ready)
+            x.record_stream(s_main)
             y = w["layer"](x)                       # act-quant + GEMM (+ all-reduce) via the layer API
-            w["y_host"].copy_(y, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(s_main)
+            s_out.wait_event(done)
+            y.record_stream(s_out)
+            with torch.cuda.stream(s_out):
+                w["y_host"].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
     def sync_all():

@@ -69,7 +69,8 @@ enum {
   B200Q_PATH_AUTO = 0,
   B200Q_PATH_SIMT_STREAM = 1, /* weight-streaming SIMT kernel, tiny M                    */
   B200Q_PATH_UMMA = 2,        /* tcgen05 kernel, tokens on the 128-row side (prefill)     */
-  B200Q_PATH_UMMA_SWAP = 3    /* tcgen05 kernel, channels on the 128-row side + split-K   */
+  B200Q_PATH_UMMA_SWAP = 3,   /* tcgen05 kernel, channels on the 128-row side + split-K   */
+  B200Q_PATH_MMA_STREAM = 4   /* weight-streaming mma.sync kernel, in-CTA split-K, M <= 64 */
 };
 
 /*

@@ -6,7 +6,8 @@ import torch
 import tiny_vllm_b200  # noqa: F401
 from tiny_vllm_b200 import _lib
 
-PATHS = {"simt": _lib.PATH_SIMT_STREAM, "umma": _lib.PATH_UMMA, "umma_swap": _lib.PATH_UMMA_SWAP}
+PATHS = {"simt": _lib.PATH_SIMT_STREAM, "umma": _lib.PATH_UMMA, "umma_swap": _lib.PATH_UMMA_SWAP,
+         "mma": _lib.PATH_MMA_STREAM}
 
 
 @contextlib.contextmanager

@@ -10,13 +10,15 @@ from tiny_vllm_b200.quantization.cuda import apply_int8_weight_only_linear
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("path", ["simt", "umma", "umma_swap", None])
+@pytest.mark.parametrize("path", ["simt", "umma", "umma_swap", "mma", None])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,N,K,bias", [(1, 64, 128, False), (5, 96, 256, True), (37, 192, 256, True),
                                         (130, 320, 1024, False), (256, 6144, 1024, False),
                                         (64, 1000, 1040, True), (300, 512, 2048, True),
                                         (513, 200, 48, False)])
 def test_matches_reference_path(path, dtype, M, N, K, bias):
+    if path == "mma" and M > 64:
+        pytest.skip("mma.sync streaming family is for M <= 64")
     q, s = O.make_weight(N, K, seed=N)
     x = O.make_activation(M, K, seed=M, dtype=dtype, outliers=False)
     b = (torch.randn(N, generator=torch.Generator().manual_seed(1)) * 0.1).to(dtype) if bias else None
@@ -34,7 +36,9 @@ def test_matches_reference_path(path, dtype, M, N, K, bias):
 
 def test_golden_cases(golden_cases):
     for c in golden_cases:
-        for path in ("simt", "umma", "umma_swap"):
+        for path in ("simt", "umma", "umma_swap", "mma"):
+            if path == "mma" and c["M"] > 64:
+                continue
             with forced_path(path):
                 y = apply_int8_weight_only_linear(c["x"].cuda(), c["q"].cuda(), c["s"].cuda(),
                                                   None if c["bias"] is None else c["bias"].cuda())
@@ -55,6 +59,10 @@ def test_all_int8_codes_expand_exactly():
             with forced_path(path):
                 y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda())
             assert torch.equal(y.float().cpu(), q.float().T), (dtype, path)
+        with forced_path("mma"):   # 64 tokens at a time
+            for r0 in range(0, K, 64):
+                y = apply_int8_weight_only_linear(x[r0:r0 + 64].cuda(), q.cuda(), s.cuda())
+                assert torch.equal(y.float().cpu(), q.float().T[r0:r0 + 64]), (dtype, r0)
 
 
 @pytest.mark.parametrize("N,K", [(4096, 1024), (1024, 2048), (6144, 1024), (1024, 3072)])

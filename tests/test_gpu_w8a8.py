@@ -37,9 +37,11 @@ SHAPES = [  # (M, N, K) — ragged tiles, single K block, K tail (K % 128 != 0),
 ]
 
 
-@pytest.mark.parametrize("path", ["simt", "umma", "umma_swap"])
-@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("path", ["simt", "umma", "umma_swap", "mma"])
+@pytest.mark.parametrize("M,N,K", SHAPES + [(17, 68, 80), (48, 1024, 3072), (64, 6144, 1024)])
 def test_int32_accumulators_bit_exact(path, M, N, K, oracle_c_lib):
+    if path == "mma" and M > 64:
+        pytest.skip("mma.sync streaming family is for M <= 64")
     if path == "simt" and M * N * K > 2e8:
         pytest.skip("SIMT family is for small token counts")
     if path == "umma_swap" and M > 512:
@@ -51,11 +53,14 @@ def test_int32_accumulators_bit_exact(path, M, N, K, oracle_c_lib):
     assert device_status_ok()
 
 
-@pytest.mark.parametrize("path", ["simt", "umma", "umma_swap", None])
+@pytest.mark.parametrize("path", ["simt", "umma", "umma_swap", "mma", None])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,N,K,bias", [(5, 96, 256, True), (130, 320, 1024, False),
-                                        (257, 512, 2048, True), (64, 1024, 3072, False)])
+                                        (257, 512, 2048, True), (64, 1024, 3072, False),
+                                        (33, 100, 272, True)])
 def test_scaled_output(path, dtype, M, N, K, bias, oracle_c_lib):
+    if path == "mma" and M > 64:
+        pytest.skip("mma.sync streaming family is for M <= 64")
     x, xq, a_s, q, s, b = problem(M, N, K, seed=N, dtype=dtype, bias=bias)
     with forced_path(path):
         y = apply_w8a8_linear(xq.cuda(), a_s.cuda(), q.cuda(), s.cuda(),
@@ -72,7 +77,9 @@ def test_scaled_output(path, dtype, M, N, K, bias, oracle_c_lib):
 
 def test_golden_cases(golden_cases):
     for c in golden_cases:
-        for path in ("simt", "umma", "umma_swap"):
+        for path in ("simt", "umma", "umma_swap", "mma"):
+            if path == "mma" and c["M"] > 64:
+                continue
             with forced_path(path):
                 acc = w8a8_int32_accumulators(c["xq"].cuda(), c["q"].cuda())
                 y = apply_w8a8_linear(c["xq"].cuda(), c["a_s"].cuda(), c["q"].cuda(), c["s"].cuda(),

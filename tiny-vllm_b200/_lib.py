@@ -38,6 +38,7 @@ PATH_AUTO = 0
 PATH_SIMT_STREAM = 1
 PATH_UMMA = 2
 PATH_UMMA_SWAP = 3
+PATH_MMA_STREAM = 4
 
 # every symbol include/b200q.h declares: name -> (restype, argtypes)
 _c = ctypes

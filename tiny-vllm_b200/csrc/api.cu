@@ -65,7 +65,8 @@ int check_dims(int M, int N, int K) {
 int auto_path_w8a8(int M, int N, int K) {
   (void)N;
   (void)K;
-  if (M <= 4) return B200Q_PATH_SIMT_STREAM;
+  if (M <= env_int("B200Q_DEBUG_SIMT_MAX_M", 0)) return B200Q_PATH_SIMT_STREAM;
+  if (M <= 64) return B200Q_PATH_MMA_STREAM;
   if (M <= 256) return B200Q_PATH_UMMA_SWAP;
   return B200Q_PATH_UMMA;
 }
@@ -74,7 +75,8 @@ int auto_path_w8a8(int M, int N, int K) {
 int auto_path_w8a16(int M, int N, int K) {
   (void)N;
   (void)K;
-  if (M <= 4) return B200Q_PATH_SIMT_STREAM;
+  if (M <= env_int("B200Q_DEBUG_SIMT_MAX_M", 0)) return B200Q_PATH_SIMT_STREAM;
+  if (M <= 64) return B200Q_PATH_MMA_STREAM;
   if (M <= 256) return B200Q_PATH_UMMA_SWAP;
   return B200Q_PATH_UMMA;
 }
@@ -93,6 +95,15 @@ int run_w8a8(GemmArgs& a) {
   const int path = resolve_path(B200Q_OP_W8A8, a.M, a.N, a.K);
   if (path == B200Q_PATH_SIMT_STREAM) {
     cudaError_t e = launch_w8a8_simt(a);
+    if (e != cudaSuccess) {
+      note_cuda_error(e);
+      return B200Q_ERR_LAUNCH;
+    }
+    return B200Q_OK;
+  }
+  if (path == B200Q_PATH_MMA_STREAM) {
+    if (!mma_decode_applicable(a.M)) return B200Q_ERR_UNSUPPORTED_SHAPE;
+    cudaError_t e = launch_w8a8_mma_decode(a);
     if (e != cudaSuccess) {
       note_cuda_error(e);
       return B200Q_ERR_LAUNCH;
@@ -245,6 +256,15 @@ int b200q_w8a16_gemm(const void* x, const int8_t* qweight, const float* scales, 
     }
     return B200Q_OK;
   }
+  if (path == B200Q_PATH_MMA_STREAM) {
+    if (!mma_decode_applicable(M)) return B200Q_ERR_UNSUPPORTED_SHAPE;
+    cudaError_t e = launch_w8a16_mma_decode(a);
+    if (e != cudaSuccess) {
+      note_cuda_error(e);
+      return B200Q_ERR_LAUNCH;
+    }
+    return B200Q_OK;
+  }
   if (path == B200Q_PATH_UMMA || path == B200Q_PATH_UMMA_SWAP) {
     UmmaPlan plan;
     if (!umma16_make_plan(M, N, K, path == B200Q_PATH_UMMA_SWAP, &plan))
@@ -275,6 +295,8 @@ const char* b200q_select_path(int op, int M, int N, int K) {
   switch (path) {
     case B200Q_PATH_SIMT_STREAM:
       return a16 ? "simt_stream_w8a16" : "simt_stream_dp4a";
+    case B200Q_PATH_MMA_STREAM:
+      return a16 ? "mma_stream_w8a16_splitk" : "mma_stream_s8_splitk";
     case B200Q_PATH_UMMA:
       if (!a16 && umma_pair_applicable(M, N, K, false)) return "umma_i8_pair_tokens256";
       return a16 ? "umma_f16_expand_tokens128" : "umma_i8_tokens128";
@@ -334,7 +356,7 @@ int b200q_device_status(void) {
 int b200q_version(void) { return B200Q_VERSION; }
 
 int b200q_debug_force_path(int path) {
-  if (path < B200Q_PATH_AUTO || path > B200Q_PATH_UMMA_SWAP) return -1;
+  if (path < B200Q_PATH_AUTO || path > B200Q_PATH_MMA_STREAM) return -1;
   return g_forced_path.exchange(path);
 }
 

@@ -62,6 +62,11 @@ cudaError_t launch_act_quant(const void* x, int64_t ldx, int x_dtype, int8_t* xq
 cudaError_t launch_w8a8_simt(const GemmArgs& a);
 cudaError_t launch_w8a16_simt(const GemmArgs& a);
 
+// gemm_mma_decode.cu: weight-streaming mma.sync kernels for M <= 64
+bool mma_decode_applicable(int M);
+cudaError_t launch_w8a8_mma_decode(const GemmArgs& a);
+cudaError_t launch_w8a16_mma_decode(const GemmArgs& a);
+
 // gemm_umma.cu
 bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan);
 // Returns a B200Q_* code.
