@@ -75,12 +75,12 @@ def test_argument_validation_needs_no_device(L):
 def test_path_names_and_workspace_queries(L):
     assert L.b200q_select_path(_lib.OP_W8A8, 8192, 4096, 1024) == b"umma_i8_pair_tokens256"
     assert L.b200q_select_path(_lib.OP_W8A8, 300, 4096, 1024) == b"umma_i8_tokens128"
-    assert L.b200q_select_path(_lib.OP_W8A8, 128, 4096, 1024) == b"umma_i8_channels128_splitk"
+    assert L.b200q_select_path(_lib.OP_W8A8, 128, 4096, 1024) == b"umma_i8_tokens128"
     assert L.b200q_select_path(_lib.OP_W8A8, 1, 4096, 1024) == b"mma_stream_s8_splitk"
     assert L.b200q_select_path(_lib.OP_W8A8, 16, 4096, 1000) == b"unsupported_shape"
     assert L.b200q_select_path(99, 1, 1, 16) == b"invalid_op"
     assert L.b200q_workspace_bytes(_lib.OP_W8A8, 8192, 4096, 1024) == 0
-    assert L.b200q_workspace_bytes(_lib.OP_W8A8, 128, 1024, 3072) > 16384
+    assert L.b200q_workspace_bytes(_lib.OP_W8A8, 128, 512, 8192) > 16384
     assert L.b200q_workspace_bytes(_lib.OP_ACT_QUANT, 16, 1024, 3072) == 0
     prev = L.b200q_debug_force_path(_lib.PATH_SIMT_STREAM)
     try:

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,N,K,bias", [(1, 64, 128, False), (5, 96, 256, True), (37, 192, 256, True),
                                         (130, 320, 1024, False), (256, 6144, 1024, False),
-                                        (64, 1000, 1040, True), (300, 512, 2048, True),
+                                        (64, 1000, 1040, True), (300, 512, 2048, True), (40, 256, 8192, False),
                                         (513, 200, 48, False)])
 def test_matches_reference_path(path, dtype, M, N, K, bias):
     if path == "mma" and M > 64:

@@ -38,7 +38,7 @@ SHAPES = [  # (M, N, K) — ragged tiles, single K block, K tail (K % 128 != 0),
 
 
 @pytest.mark.parametrize("path", ["simt", "umma", "umma_swap", "mma"])
-@pytest.mark.parametrize("M,N,K", SHAPES + [(17, 68, 80), (48, 1024, 3072), (64, 6144, 1024)])
+@pytest.mark.parametrize("M,N,K", SHAPES + [(17, 68, 80), (48, 1024, 3072), (64, 6144, 1024), (40, 256, 8192), (300, 384, 12288)])
 def test_int32_accumulators_bit_exact(path, M, N, K, oracle_c_lib):
     if path == "mma" and M > 64:
         pytest.skip("mma.sync streaming family is for M <= 64")
@@ -154,20 +154,20 @@ def test_baseline_decode_shapes(M, N, K, oracle_c_lib):
 
 def test_repeated_split_k_calls_leave_workspace_clean():
     # the split-K counters must return to zero: same call three times, same answer
-    _, xq, a_s, q, s, _ = problem(48, 1024, 3072, seed=9)
+    _, xq, a_s, q, s, _ = problem(48, 256, 8192, seed=9)
     expect = O.w8a8_int32_accumulators(xq, q)
     with forced_path("umma_swap"):
-        assert _lib.lib().b200q_workspace_bytes(_lib.OP_W8A8, 48, 1024, 3072) > 0
+        assert _lib.lib().b200q_workspace_bytes(_lib.OP_W8A8, 48, 256, 8192) > 0
         for _ in range(3):
             assert torch.equal(w8a8_int32_accumulators(xq.cuda(), q.cuda()).cpu(), expect)
 
 
 def test_workspace_too_small_is_an_error():
-    _, xq, a_s, q, s, _ = problem(48, 1024, 3072, seed=9)
+    _, xq, a_s, q, s, _ = problem(48, 256, 8192, seed=9)
     gx, gq = xq.cuda(), q.cuda()
-    acc = torch.empty(48, 1024, dtype=torch.int32, device="cuda")
+    acc = torch.empty(48, 256, dtype=torch.int32, device="cuda")
     L = _lib.lib()
     with forced_path("umma_swap"):
-        rc = L.b200q_w8a8_gemm_i32(gx.data_ptr(), gq.data_ptr(), acc.data_ptr(), 48, 1024, 3072,
+        rc = L.b200q_w8a8_gemm_i32(gx.data_ptr(), gq.data_ptr(), acc.data_ptr(), 48, 256, 8192,
                                    None, 0, torch.cuda.current_stream().cuda_stream)
     assert rc == _lib.ERR_WORKSPACE

@@ -29,8 +29,8 @@ def call_noalloc(xq, a_s, q, s, bias, dtype):
     return rc, y
 
 
-@pytest.mark.parametrize("M,N,K,with_bias", [(48, 1024, 3072, False), (16, 1024, 2048, True),
-                                             (200, 512, 1024, False)])
+@pytest.mark.parametrize("M,N,K,with_bias", [(48, 256, 8192, False), (16, 512, 8192, True),
+                                             (200, 256, 16384, False)])
 def test_matches_the_workspace_entry_point_on_consecutive_calls(M, N, K, with_bias):
     L = _lib.lib()
     q, s = O.make_weight(N, K, seed=N + K)
@@ -72,7 +72,7 @@ def test_prefill_sized_call_needs_no_scratch_and_matches():
 
 def test_refuses_problems_beyond_the_built_in_scratch_and_bad_arguments():
     L = _lib.lib()
-    M, N, K = 256, 6144, 1024      # split-K partial tiles of this shape exceed 8 MiB
+    M, N, K = 256, 9216, 8192      # split-K partial tiles of this shape exceed 8 MiB
     xq = torch.zeros(M, K, dtype=torch.int8, device="cuda")
     q = torch.zeros(N, K, dtype=torch.int8, device="cuda")
     a_s = torch.ones(M, device="cuda")

@@ -66,8 +66,7 @@ int auto_path_w8a8(int M, int N, int K) {
   (void)N;
   (void)K;
   if (M <= env_int("B200Q_DEBUG_SIMT_MAX_M", 0)) return B200Q_PATH_SIMT_STREAM;
-  if (M <= 64) return B200Q_PATH_MMA_STREAM;
-  if (M <= 256) return B200Q_PATH_UMMA_SWAP;
+  if (M <= 32) return B200Q_PATH_MMA_STREAM;
   return B200Q_PATH_UMMA;
 }
 
@@ -76,8 +75,7 @@ int auto_path_w8a16(int M, int N, int K) {
   (void)N;
   (void)K;
   if (M <= env_int("B200Q_DEBUG_SIMT_MAX_M", 0)) return B200Q_PATH_SIMT_STREAM;
-  if (M <= 64) return B200Q_PATH_MMA_STREAM;
-  if (M <= 256) return B200Q_PATH_UMMA_SWAP;
+  if (M <= 32) return B200Q_PATH_MMA_STREAM;
   return B200Q_PATH_UMMA;
 }
 

@@ -585,7 +585,7 @@ bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan) {
   if (!swap && pl.rows_b >= 256) {
     const int ta = (pl.rows_a + kTileA - 1) / kTileA;
     double best = 1e30;
-    for (int cand : {256, 128}) {
+    for (int cand : {256, 128, 64}) {
       const int tiles = ta * ((pl.rows_b + cand - 1) / cand);
       const int waves = (tiles + sms - 1) / sms;
       const double cost = waves * (cand + 32.0);
@@ -602,11 +602,14 @@ bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan) {
   pl.tiles_b = (pl.rows_b + bn - 1) / bn;
   const long long tiles = static_cast<long long>(pl.tiles_a) * pl.tiles_b;
   if (tiles > 1 << 22) return false;
+  // Split K over CTAs only when few tiles would each have a long K loop: handing partial
+  // tiles over through global memory costs several microseconds, more than streaming a
+  // few hundred KB of weights through one SM.
   int splits = 1;
-  if (tiles < sms) {
+  if (tiles * 2 <= sms && pl.k_blocks >= 128) {
     splits = static_cast<int>(sms / tiles);
-    splits = std::min(splits, std::max(1, pl.k_blocks / 4));
-    splits = std::min(splits, 16);
+    splits = std::min(splits, pl.k_blocks / 64);
+    splits = std::min(splits, 8);
   }
   splits = env_int("B200Q_DEBUG_SPLITS", splits);
   if (splits < 1) splits = 1;
