@@ -347,6 +347,8 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else if (warp == 1) {
     if (lane == 0) {
       // ------------------------------------------------------- UMMA issuer
+      // A and B must have the same element type in kind::f16 (a bf16 x fp16 descriptor was
+      // tried once and faulted), so the weights are expanded to the activation type.
       const uint32_t fmt = p.is_bf16 ? 1u : 0u;
       const uint32_t idesc = ptx::umma_idesc(1u, fmt, kTileA, static_cast<uint32_t>(p.bn));
       int stage = 0, cb = 0;
