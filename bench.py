@@ -200,6 +200,12 @@ def run_gpu_arm(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     tp = world
+    comm = None
+    if tp > 1 and not args.nccl_allreduce:
+        # partial outputs of the row-parallel layers live in symmetric memory and are summed
+        # in place over NVLink by b200q_tp_allreduce (one slot per row-parallel layer)
+        from tiny_vllm_b200.layers.tp_comm import PeerAllReduce
+        comm = PeerAllReduce(max_bytes=TOKENS * 1024 * 2, slots=2)
     L = _lib.lib()
     stream = torch.cuda.current_stream().cuda_stream
 
@@ -227,7 +233,8 @@ def run_gpu_arm(args):
             "x_host": x_local.pin_memory(), "x": x_local.to(dev),
             "xq": torch.empty(TOKENS, k_loc, dtype=torch.int8, device=dev),
             "a_s": torch.empty(TOKENS, dtype=torch.float32, device=dev),
-            "y": torch.empty(TOKENS, n_loc, dtype=torch.bfloat16, device=dev),
+            "y": (comm.buffer((TOKENS, n_loc), torch.bfloat16) if (comm is not None and split == "row")
+                  else torch.empty(TOKENS, n_loc, dtype=torch.bfloat16, device=dev)),
             "y_host": torch.empty(TOKENS, n_loc, dtype=torch.bfloat16, device="cpu").pin_memory(),
             "layer": layer, "ops": 2.0 * TOKENS * k_loc * n_loc,
         })
@@ -252,7 +259,10 @@ def run_gpu_arm(args):
                 e1.record()
                 events.append((w["name"], e0, e1))
             if w["split"] == "row" and tp > 1:
-                dist.all_reduce(w["y"])
+                if comm is not None:
+                    comm.all_reduce_(w["y"])
+                else:
+                    dist.all_reduce(w["y"])
 
     # End-to-end step: pinned host activations -> device -> layer API -> pinned host outputs.
     # Uploads, compute and downloads run on three streams so that the two copy engines and
@@ -369,6 +379,8 @@ def run_gpu_arm(args):
             "config": {"workload": "configs[1]: W8A8 prefill GEMM sweep, M=8192, Qwen3-0.6B projections "
                                    "(qkv 1024->4096, o 2048->1024, gate_up 1024->6144, down 3072->1024)",
                        "tokens": TOKENS, "parallelism": f"tp{world}",
+                       "allreduce": ("none" if world == 1 else
+                                     "b200q_tp_allreduce (peer memory)" if comm is not None else "nccl"),
                        "l2": "no flush: one step touches about 450 MB (activations, int8 copies, outputs), "
                              "more than the 126 MB L2"},
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
@@ -389,6 +401,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nccl-allreduce", action="store_true",
+                    help="sum row-parallel outputs with NCCL instead of the peer-memory kernel")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -166,6 +166,21 @@ int b200q_debug_force_path(int path);
 uint64_t b200q_launch_count(void);
 
 /*
+ * In-place sum all-reduce of a 16-bit tensor over the tensor-parallel ranks of one node,
+ * through peer memory (NVLink).  Replaces `dist.all_reduce(y)` after a row-parallel
+ * linear (nanovllm/layers/linear.py:274-275) for tensors that live in a symmetric
+ * allocation.  peer_buffers[r] / peer_flag_pads[r] are HOST arrays of `world` DEVICE
+ * addresses, as mapped into the calling process: rank r's tensor (same element offset on
+ * every rank) and rank r's flag pad (>= 256 bytes, zero-filled once before the first
+ * call, never touched by the caller afterwards).  Every rank must make the same sequence
+ * of calls; n_elems must be a multiple of 8; world <= 8.  fp32 accumulation in rank
+ * order, so all ranks receive bit-identical results.  Waits on peers are bounded (about a
+ * second), after which the call's kernel records a status (b200q_device_status) and ends.
+ */
+int b200q_tp_allreduce(void* const* peer_buffers, void* const* peer_flag_pads, int rank, int world,
+                       size_t n_elems, int dtype, void* stream);
+
+/*
  * W8A8 linear for callers that have no way to hand over scratch memory.
  * (No counterpart in the reference: its kernels never need scratch.)
  *

@@ -1,0 +1,240 @@
+// Sum all-reduce of a 16-bit tensor across the tensor-parallel ranks of one node, over
+// peer memory (NVLink / NVSwitch), in place — the exchange step after a row-parallel
+// linear (reference: dist.all_reduce(y) at nanovllm/layers/linear.py:274-275).
+//
+// Every rank passes the device addresses of all ranks' buffers (symmetric allocation:
+// same size, mapped into every process) and of all ranks' flag pads.  Two-shot scheme:
+//   1. flag barrier A: "my partial result is complete" (guaranteed by stream order on the
+//      sender, announced by one release store per peer);
+//   2. rank r sums chunk range r of all buffers with 16-byte peer loads (fp32 accumulate,
+//      ranks added in index order, so every rank ends up with bit-identical values) and
+//      writes the sums into chunk range r of EVERY rank's buffer with 16-byte peer stores;
+//   3. flag barrier B: the last CTA of each rank announces "my writes are done" and waits
+//      for the same announcement from every peer before the kernel ends.
+// Flags are monotonically increasing epochs (one per call), never reset.  Every spin is
+// bounded: on expiry the kernel records a status code and returns, nothing waits for ever.
+// Plain loads and stores only — no TMA, no multicast.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "common.h"
+
+namespace b200q {
+namespace {
+
+constexpr int kMaxWorld = 8;
+constexpr int kThreads = 512;
+// 32-bit slots of a rank's flag pad
+constexpr int kSlotEpoch = 0;     // number of completed calls
+constexpr int kSlotCounter = 1;   // CTAs of this rank that finished the reduce phase
+constexpr int kSlotA = 16;        // [kSlotA + src]: src's input is ready (epoch)
+constexpr int kSlotB = 32;        // [kSlotB + src]: src's writes are done (epoch)
+constexpr long long kSpinLimitCycles = 2000000000LL;  // about one second
+
+struct Params {
+  void* buf[kMaxWorld];
+  unsigned int* pad[kMaxWorld];
+  int rank, world;
+  unsigned long long n_chunks;  // 16-byte chunks in the tensor
+  int is_bf16;
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer16(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_peer16(void* p, const uint4 v) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+// Waits until the flag holds at least `epoch` (wrap-safe).  False when the limit ran out.
+__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int epoch) {
+  const long long t0 = clock64();
+  while (static_cast<int>(ld_acquire_sys(flag) - epoch) < 0) {
+    if (clock64() - t0 > kSpinLimitCycles) return false;
+  }
+  return true;
+}
+
+template <bool BF16>
+__device__ __forceinline__ void accumulate(float (&acc)[8], const uint4 v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f;
+    if (BF16) {
+      f = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
+    } else {
+      f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    }
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint4 pack(const float (&acc)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (BF16) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+      const __half2 h = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// W = compile-time bound on the number of ranks, U = chunks per thread per iteration: all
+// U * world loads of an iteration are issued before the first use, so that enough bytes are
+// in flight to cover the NVLink round trip (small worlds need the larger U).
+template <bool BF16, int W, int U>
+__global__ void __launch_bounds__(kThreads)
+tp_allreduce_kernel(const Params p) {
+  __shared__ unsigned int s_epoch;
+  __shared__ int s_flag;  // 0 ok, 1 = a wait gave up, 2 = this CTA is the rank's last
+  unsigned int* my_pad = p.pad[p.rank];
+  if (threadIdx.x == 0) {
+    s_epoch = *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) + 1u;
+    s_flag = 0;
+  }
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
+
+  // ---- barrier A: every rank's partial result is complete
+  if (threadIdx.x < p.world) {
+    if (blockIdx.x == 0) st_release_sys(p.pad[threadIdx.x] + kSlotA + p.rank, epoch);
+    if (!wait_flag(my_pad + kSlotA + threadIdx.x, epoch)) s_flag = 1;
+  }
+  __syncthreads();
+  const bool ok = s_flag == 0;
+
+  // ---- reduce my chunk range, publish it to every rank
+  if (ok) {
+    const unsigned long long per_rank = (p.n_chunks + p.world - 1) / p.world;
+    const unsigned long long begin = per_rank * p.rank;
+    const unsigned long long end = min(p.n_chunks, begin + per_rank);
+    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * kThreads;
+    for (unsigned long long i0 = begin + static_cast<unsigned long long>(blockIdx.x) * kThreads +
+                                 threadIdx.x;
+         i0 < end; i0 += stride * U) {
+      uint4 v[U][W];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const unsigned long long i = i0 + stride * u;
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+          if (r < p.world && i < end) v[u][r] = ld_peer16(static_cast<const uint4*>(p.buf[r]) + i);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const unsigned long long i = i0 + stride * u;
+        if (i >= end) break;
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+          if (r < p.world) accumulate<BF16>(acc, v[u][r]);
+        const uint4 out = pack<BF16>(acc);
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+          if (r < p.world) st_peer16(static_cast<uint4*>(p.buf[r]) + i, out);
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+
+  // ---- barrier B: by the last CTA of this rank to get here
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(my_pad + kSlotCounter, 1u);
+    if (done == gridDim.x - 1) {
+      my_pad[kSlotCounter] = 0u;
+      if (s_flag == 0) s_flag = 2;
+    }
+  }
+  __syncthreads();
+  if (s_flag == 2) {
+    __threadfence_system();
+    if (threadIdx.x < p.world) {
+      st_release_sys(p.pad[threadIdx.x] + kSlotB + p.rank, epoch);
+      if (!wait_flag(my_pad + kSlotB + threadIdx.x, epoch)) atomicCAS(p.status, 0, 0x502);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
+  } else if (s_flag == 1 && threadIdx.x == 0) {
+    atomicCAS(p.status, 0, 0x501);
+    // keep the call count in step with the peers even though this call failed
+    if (blockIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
+  }
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" int b200q_tp_allreduce(void* const* peer_buffers, void* const* peer_flag_pads, int rank,
+                                  int world, size_t n_elems, int dtype, void* stream) {
+  using namespace b200q;
+  if (peer_buffers == nullptr || peer_flag_pads == nullptr) return B200Q_ERR_NULL_POINTER;
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return B200Q_ERR_BAD_ARGUMENT;
+  if (dtype != B200Q_DTYPE_F16 && dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  if (n_elems == 0 || (n_elems % 8) != 0) return B200Q_ERR_UNSUPPORTED_SHAPE;  // 16-byte chunks
+  Params p{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_buffers[r] == nullptr || peer_flag_pads[r] == nullptr) return B200Q_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(peer_buffers[r]) & 15u) != 0) return B200Q_ERR_MISALIGNED;
+    p.buf[r] = peer_buffers[r];
+    p.pad[r] = static_cast<unsigned int*>(peer_flag_pads[r]);
+  }
+  if (device_cc_major() != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+  p.rank = rank;
+  p.world = world;
+  p.n_chunks = n_elems / 8;
+  p.is_bf16 = dtype == B200Q_DTYPE_BF16;
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return B200Q_ERR_LAUNCH;
+  const unsigned long long per_rank = (p.n_chunks + world - 1) / world;
+  long long blocks = static_cast<long long>((per_rank + kThreads * 4 - 1) / (kThreads * 4));
+  if (blocks < 1) blocks = 1;
+  if (blocks > sm_count()) blocks = sm_count();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = static_cast<int>(blocks);
+#define B200Q_AR_LAUNCH(BF, W, U) tp_allreduce_kernel<BF, W, U><<<grid, kThreads, 0, st>>>(p)
+  if (p.is_bf16) {
+    if (world <= 2) B200Q_AR_LAUNCH(true, 2, 4);
+    else if (world <= 4) B200Q_AR_LAUNCH(true, 4, 2);
+    else B200Q_AR_LAUNCH(true, 8, 1);
+  } else {
+    if (world <= 2) B200Q_AR_LAUNCH(false, 2, 4);
+    else if (world <= 4) B200Q_AR_LAUNCH(false, 4, 2);
+    else B200Q_AR_LAUNCH(false, 8, 1);
+  }
+#undef B200Q_AR_LAUNCH
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  count_launch();
+  return B200Q_OK;
+}

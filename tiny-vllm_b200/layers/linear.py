@@ -36,6 +36,20 @@ _QUANT_METHODS = {"int8": Int8WeightOnlyQuantMethod, "w8a8": W8A8QuantMethod}
 _SCALE_NAMES = ("scales", "w_scales")
 
 
+# Optional replacement for the NCCL all-reduce after row-parallel layers: an object with
+# ``buffer(shape, dtype)`` and ``all_reduce_(tensor)`` (layers.tp_comm.PeerAllReduce).
+_peer_all_reduce = None
+
+
+def set_tp_all_reduce(comm) -> None:
+    """Routes the sum after every RowParallelLinear through ``comm`` (peer-memory kernel)
+    instead of ``dist.all_reduce``; ``None`` restores NCCL.  With a communicator the layer's
+    result lives in one of its rotating symmetric slots: it stays valid until that many
+    further row-parallel calls have been made."""
+    global _peer_all_reduce
+    _peer_all_reduce = comm
+
+
 def divide(numerator: int, denominator: int) -> int:
     quotient, rest = divmod(numerator, denominator)
     assert rest == 0, f"{numerator} is not divisible by {denominator}"
@@ -257,5 +271,11 @@ class RowParallelLinear(LinearBase):
             # ``None`` bias lets the quant method pick ``self.bias`` on every rank.
             y = self.quant_method.apply(x, self, bias)
         if self.tp_size > 1:
+            comm = _peer_all_reduce
+            if comm is not None and y.is_cuda and y.numel() % 8 == 0 \
+                    and y.numel() * y.element_size() <= comm.slot_bytes:
+                shared = comm.buffer(y.shape, y.dtype)
+                shared.copy_(y)
+                return comm.all_reduce_(shared)
             dist.all_reduce(y)
         return y

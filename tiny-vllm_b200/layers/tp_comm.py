@@ -1,0 +1,89 @@
+"""Tensor-parallel exchange step after a row-parallel linear.
+
+The reference sums the per-rank partial outputs with ``dist.all_reduce(y)`` (NCCL,
+``nanovllm/layers/linear.py:274-275``).  This module keeps that as the default and adds
+an in-place all-reduce over peer memory (``b200q_tp_allreduce``: NVLink loads/stores
+between the ranks' buffers, bounded flag waits) for tensors that live in a symmetric
+allocation — memory of the same size on every rank, mapped into every process with
+``torch.distributed._symmetric_memory``.
+
+Usage (every rank, same order of calls)::
+
+    comm = PeerAllReduce(max_bytes=64 << 20)          # once, after init_process_group
+    y = comm.buffer((tokens, hidden), torch.bfloat16)  # write the partial result here
+    ...                                                # e.g. the GEMM's output pointer
+    comm.all_reduce_(y)                                # y now holds the sum on every rank
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+
+_DTYPE_IDS = {torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16}
+_PAD_BYTES = 4096
+
+
+class PeerAllReduce:
+    """Owns one symmetric data buffer and one symmetric flag pad for a process group."""
+
+    def __init__(self, max_bytes: int, group=None, slots: int = 2):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if not dist.is_initialized():
+            raise RuntimeError("PeerAllReduce needs an initialised process group")
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        if self.world > 8:
+            raise RuntimeError("PeerAllReduce supports up to 8 ranks (one node)")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.slot_bytes = (max_bytes + 255) // 256 * 256
+        self.slots = slots
+        self._next = 0
+        name = self.group.group_name
+        self._data = symm_mem.empty(self.slot_bytes * slots, dtype=torch.uint8, device=dev)
+        self._data_hdl = symm_mem.rendezvous(self._data, name)
+        self._pad = symm_mem.empty(_PAD_BYTES, dtype=torch.uint8, device=dev)
+        self._pad.zero_()
+        self._pad_hdl = symm_mem.rendezvous(self._pad, name)
+        torch.cuda.synchronize()
+        dist.barrier(self.group)           # every pad is zero before anyone signals
+        self._data_ptrs = [int(p) for p in self._data_hdl.buffer_ptrs]
+        pads = [int(p) for p in self._pad_hdl.buffer_ptrs]
+        self._pad_arr = (ctypes.c_void_p * self.world)(*pads)
+
+    def buffer(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A tensor inside the symmetric allocation (slots are handed out round-robin, so a
+        tensor stays valid until ``slots`` further buffers have been requested)."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        if nbytes > self.slot_bytes:
+            raise RuntimeError(f"tensor of {nbytes} bytes exceeds the symmetric slot ({self.slot_bytes})")
+        off = self._next * self.slot_bytes
+        self._next = (self._next + 1) % self.slots
+        return self._data[off:off + nbytes].view(dtype).view(*shape)
+
+    def owns(self, t: torch.Tensor) -> bool:
+        base = self._data.data_ptr()
+        return t.is_contiguous() and base <= t.data_ptr() < base + self._data.numel()
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        """Sums ``t`` (a tensor from :meth:`buffer`, same slot on every rank) over the group,
+        in place, on the current stream."""
+        if not self.owns(t):
+            raise RuntimeError("all_reduce_ needs a contiguous tensor obtained from buffer()")
+        if t.dtype not in _DTYPE_IDS or t.numel() % 8 != 0:
+            raise RuntimeError("all_reduce_ supports fp16/bf16 tensors with a multiple of 8 elements")
+        off = t.data_ptr() - self._data.data_ptr()
+        bufs = (ctypes.c_void_p * self.world)(*[p + off for p in self._data_ptrs])
+        rc = _lib.lib().b200q_tp_allreduce(bufs, self._pad_arr, self.rank, self.world, t.numel(),
+                                           _DTYPE_IDS[t.dtype],
+                                           torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "b200q_tp_allreduce", f"n={t.numel()} world={self.world}")
+        return t
