@@ -72,6 +72,34 @@ def _worker(rank, world, port, out_dir):
             torch.cuda.synchronize()
             notes.append(f"{name} 16 MiB all-reduce: {e0.elapsed_time(e1) / 20 * 1e3:.1f} us")
         ok = ok and _lib.lib().b200q_device_status() == 0
+        # a quantized row-parallel layer: NCCL sum vs peer-memory sum vs the CPU oracle
+        from oracle import quant_linear_oracle as O
+        from tiny_vllm_b200.layers import linear as LL
+        K, N, M = 512 * world, 384, 96
+        q, s = O.make_weight(N, K, seed=11)
+        x = O.make_activation(M, K, seed=12)
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(torch.bfloat16)
+        with torch.device("cuda"):
+            layer = LL.RowParallelLinear(K, N, quantization="w8a8")
+        torch.set_default_dtype(prev)
+        layer.qweight.weight_loader(layer.qweight, q)
+        layer.w_scales.weight_loader(layer.w_scales, s)
+        x_local = x.chunk(world, dim=1)[rank].contiguous().cuda()
+        y_nccl = layer(x_local).clone()
+        LL.set_tp_all_reduce(comm)
+        y_peer = layer(x_local).clone()
+        LL.set_tp_all_reduce(None)
+        ref = torch.zeros(M, N)
+        for r in range(world):               # what each rank computes, summed in fp32
+            xq, a_s = O.quantize_per_row_dynamic(x.chunk(world, dim=1)[r].contiguous())
+            acc = O.w8a8_int32_accumulators(xq, q.chunk(world, dim=1)[r].contiguous(), use_c=False)
+            ref += O.w8a8_native_epilogue(acc, a_s, s, None, torch.bfloat16).float()
+        same = torch.equal(y_peer.cpu().view(torch.int16), ref.to(torch.bfloat16).view(torch.int16))
+        m = O.tensor_metrics(y_nccl, y_peer)
+        ok = ok and same and m["relative_l2"] < 1e-2
+        if not same:
+            notes.append(f"row-parallel layer: peer sum differs from rank-ordered fp32 sum, {m}")
     except Exception as exc:  # noqa: BLE001
         ok = False
         notes.append(repr(exc))

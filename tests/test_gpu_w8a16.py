@@ -65,6 +65,29 @@ def test_all_int8_codes_expand_exactly():
                 assert torch.equal(y.float().cpu(), q.float().T[r0:r0 + 64]), (dtype, r0)
 
 
+@pytest.mark.parametrize("M,N,K,dtype,bias", [(2500, 2056, 272, torch.bfloat16, True),
+                                              (2305, 2304, 1024, torch.float16, False)])
+def test_prefill_kernel_ragged_edges(M, N, K, dtype, bias):
+    q, s = O.make_weight(N, K, seed=N)
+    x = O.make_activation(M, K, seed=M, dtype=dtype, outliers=False)
+    b = (torch.randn(N, generator=torch.Generator().manual_seed(1)) * 0.1).to(dtype) if bias else None
+    y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda())
+    m = O.tensor_metrics(O.w8a16_native_reference(x, q, s, b), y)
+    assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
+    assert device_status_ok()
+
+
+def test_prefill_kernel_expands_every_code_exactly():
+    K, M, N = 256, 2560, 2048
+    q = torch.stack([torch.roll(torch.arange(-128, 128, dtype=torch.int16).to(torch.int8), i)
+                     for i in range(N)])
+    s = torch.ones(N)
+    for dtype in (torch.bfloat16, torch.float16):
+        x = torch.eye(K, dtype=dtype).repeat(M // K, 1)        # row m selects weight column m % K
+        y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda())
+        assert torch.equal(y.float().cpu(), q.float().T.repeat(M // K, 1)), dtype
+
+
 @pytest.mark.parametrize("N,K", [(4096, 1024), (1024, 2048), (6144, 1024), (1024, 3072)])
 def test_baseline_prefill_shapes_full_size(N, K):
     # M = 8192: sampled rows against the oracle, all rows through linearity in x
