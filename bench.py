@@ -394,6 +394,89 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_shape_sweep(args):
+    """Secondary tables (not the headline line): per-shape kernel times for the decode shapes
+    M in {1, 16, 128, 512} and the prefill shape M = 8192 of both GEMM kinds and for the
+    activation quantiser.  Launches are replayed from a CUDA graph (no host overhead in the
+    numbers) over rotating buffers larger than L2.  Prints one JSON line."""
+    import tiny_vllm_b200  # noqa: F401
+    from tiny_vllm_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200)")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    L = _lib.lib()
+    ws = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    peaks = load_peaks()
+
+    def time_op(op, M, N, K, iters):
+        nbuf = max(2, min(16, int(300e6 // max(1, N * K + 2 * M * N)) + 1))
+        xq = [torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev) for _ in range(nbuf)]
+        xb = [torch.randn(M, K, dtype=torch.bfloat16, device=dev) for _ in range(nbuf)]
+        wq = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(nbuf)]
+        a_s = torch.rand(M, device=dev)
+        w_s = torch.rand(N, device=dev)
+        y = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(nbuf)]
+        side = torch.cuda.Stream(device=dev)
+
+        def call(i, st):
+            j = i % nbuf
+            if op == "w8a8":
+                rc = L.b200q_w8a8_gemm(xq[j].data_ptr(), a_s.data_ptr(), wq[j].data_ptr(), w_s.data_ptr(),
+                                       None, y[j].data_ptr(), M, N, K, _lib.DTYPE_BF16, ws.data_ptr(),
+                                       ws.numel(), st)
+            elif op == "w8a16":
+                rc = L.b200q_w8a16_gemm(xb[j].data_ptr(), wq[j].data_ptr(), w_s.data_ptr(), None,
+                                        y[j].data_ptr(), M, N, K, _lib.DTYPE_BF16, ws.data_ptr(),
+                                        ws.numel(), st)
+            else:
+                rc = L.b200q_act_quant_i8(xb[j].data_ptr(), K, _lib.DTYPE_BF16, xq[j].data_ptr(),
+                                          a_s.data_ptr(), M, K, st)
+            _lib.check(rc, op)
+
+        for i in range(3):
+            call(i, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(iters):
+                    call(i, side.cuda_stream)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / iters
+
+    results = []
+    shapes = [(name, n, k) for name, k, n, _ in PROJECTIONS]
+    for op in ("w8a8", "w8a16"):
+        for M in (1, 16, 128, 512, TOKENS):
+            for name, N, K in shapes:
+                us = time_op(op, M, N, K, 20 if M == TOKENS else 100)
+                in_bytes = M * K * (1 if op == "w8a8" else 2)
+                alg_bytes = in_bytes + N * K + 4 * N + 2 * M * N + (4 * M if op == "w8a8" else 0)
+                ops = 2.0 * M * N * K
+                results.append({"op": op, "proj": name, "M": M, "N": N, "K": K, "us": round(us, 2),
+                                "tops": round(ops / us / 1e6, 1),
+                                "algorithmic_gbs": round(alg_bytes / us / 1e3, 1),
+                                "hbm_frac": round(alg_bytes / us / 1e3 / peaks["hbm_gbs"], 3),
+                                "path": L.b200q_select_path(_lib.OP_W8A8 if op == "w8a8" else _lib.OP_W8A16,
+                                                            M, N, K).decode()})
+    for name, N, K in shapes:
+        us = time_op("act_quant", TOKENS, N, K, 50)
+        b = 3 * TOKENS * K + 4 * TOKENS
+        results.append({"op": "act_quant", "proj": name, "M": TOKENS, "K": K, "us": round(us, 2),
+                        "algorithmic_gbs": round(b / us / 1e3, 1),
+                        "hbm_frac": round(b / us / 1e3 / peaks["hbm_gbs"], 3)})
+    print(json.dumps({"mode": "shape_sweep", "peaks": peaks, "device_status": L.b200q_device_status(),
+                      "results": results}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -403,7 +486,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="sum row-parallel outputs with NCCL instead of the peer-memory kernel")
+    ap.add_argument("--mode", default="headline", choices=["headline", "shape_sweep"],
+                    help="shape_sweep prints per-shape kernel times (decode and prefill shapes)")
     args = ap.parse_args()
+    if args.mode == "shape_sweep":
+        run_shape_sweep(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -1,9 +1,9 @@
 """Generates tests/golden/quant_linear_golden.npz from the REFERENCE's own Python code.
 
-Run in a container that has the reference checkout (default /root/reference, or pass
-its path as argv[1]):
+Run where a checkout of the reference (daiyu1111/tiny-vllm) is available, passing its path
+(or set NANOVLLM_REFERENCE):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It imports ``nanovllm.quantization.utils`` and ``nanovllm.quantization.cuda`` from
 the reference, unmodified, runs them on CPU on seeded synthetic inputs and stores
@@ -37,7 +37,11 @@ def bits16(t: torch.Tensor) -> np.ndarray:
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("NANOVLLM_REFERENCE")
+    if not where:
+        raise SystemExit("usage: make_golden.py /path/to/reference-checkout")
+    ref = Path(where)
     sys.path.insert(0, str(ref))
     from nanovllm.quantization.cuda import int8_weight_only_linear_fallback, w8a8_linear_fallback
     from nanovllm.quantization.utils import quantize_int8_per_channel, quantize_int8_per_row_dynamic
