@@ -341,13 +341,13 @@ def run_gpu_arm(args):
     int8_peak = 2.0 * peaks["bf16_sustained"]
     achieved = gemm_ops_total / (gemm_ms_total * 1e-3) / 1e12
     # DRAM bytes per launch from the ncu capture summarised in
-    # profiles/w8a8_umma_kernel_prefill_sweep_m8192.md (mean of the four shapes, TP=1 only)
-    traffic = 130.2e6 / 4 if world == 1 else None
+    # profiles/w8a8_umma_pair_kernel_prefill_sweep_m8192.md (mean of the four shapes, TP=1 only)
+    traffic = 127.1e6 / 4 if world == 1 else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                 "frac": achieved / int8_peak, "traffic": traffic,
                 "traffic_note": "dram__bytes_read+write per launch, mean over the 4 shapes; algorithmic "
                                 "mean is 66.6 MB, the difference is output still dirty in L2 at kernel end",
-                "kernel": "w8a8_umma_kernel (tcgen05 kind::i8)",
+                "kernel": "w8a8_umma_pair_kernel (tcgen05 cta_group::2 kind::i8)" if world == 1 else "w8a8_umma kernels (tcgen05 kind::i8)",
                 "peak_note": f"2 x {peaks['source']} sustained bf16 dense TFLOP/s ({peaks['bf16_sustained']}); "
                              "int8 is the double-rate kind; nominal 4500"}
 
