@@ -205,7 +205,16 @@ def run_gpu_arm(args):
         # partial outputs of the row-parallel layers live in symmetric memory and are summed
         # in place over NVLink by b200q_tp_allreduce (one slot per row-parallel layer)
         from tiny_vllm_b200.layers.tp_comm import PeerAllReduce
-        comm = PeerAllReduce(max_bytes=TOKENS * 1024 * 2, slots=2)
+        try:
+            comm = PeerAllReduce(max_bytes=TOKENS * 1024 * 2, slots=2)
+            made = 1
+        except Exception as exc:  # symmetric memory not available on this box
+            print(f"[bench] rank {rank}: peer all-reduce unavailable ({exc!r}); using NCCL", file=sys.stderr)
+            comm, made = None, 0
+        agree = torch.tensor([made], device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)     # all ranks take the same route
+        if int(agree.item()) == 0:
+            comm = None
     L = _lib.lib()
     stream = torch.cuda.current_stream().cuda_stream
 

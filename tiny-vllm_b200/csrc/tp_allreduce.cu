@@ -51,7 +51,9 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
 }
 __device__ __forceinline__ uint4 ld_peer16(const void* p) {
   uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+  // weak load, not cached in L1: each address is read once per call and the call's first
+  // barrier orders it after the peers' writes
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p)
                : "memory");
