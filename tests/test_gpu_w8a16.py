@@ -108,6 +108,28 @@ def test_baseline_prefill_shapes_full_size(N, K):
     assert device_status_ok()
 
 
+@pytest.mark.parametrize("M", [16, 300])
+@pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 12288)])
+def test_qwen3_8b_shapes(M, N, K):
+    q, s = O.make_weight(N, K, seed=N)
+    x = O.make_activation(M, K, seed=M, outliers=False)
+    y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda())
+    m = O.tensor_metrics(O.w8a16_native_reference(x, q, s), y)
+    assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
+    m = O.tensor_metrics(O.w8a16_dequant_matmul(x, q, s), y)
+    assert m["relative_l2"] <= 1e-2 and m["cosine_similarity"] >= 0.9999, m
+    assert device_status_ok()
+
+
+def test_non_contiguous_activations_are_accepted():
+    q, s = O.make_weight(64, 128)
+    big = O.make_activation(24, 256).cuda()
+    view = big[:, 64:192]                       # row pitch 256, offset 64
+    y = apply_int8_weight_only_linear(view, q.cuda(), s.cuda())
+    m = O.tensor_metrics(O.w8a16_native_reference(view.cpu(), q, s), y)
+    assert m["relative_l2"] <= 4e-3, m
+
+
 def test_leading_dimensions_are_kept():
     q, s = O.make_weight(64, 128)
     x = O.make_activation(24, 128).view(2, 3, 4, 128)

@@ -152,6 +152,34 @@ def test_baseline_decode_shapes(M, N, K, oracle_c_lib):
     assert device_status_ok()
 
 
+@pytest.mark.parametrize("M", [16, 300])
+@pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 12288)])
+def test_qwen3_8b_shapes(M, N, K, oracle_c_lib):
+    # the larger model of the engine configs: qkv (4096 -> 6144) and down (12288 -> 4096);
+    # K = 12288 is the longest reduction (|acc| up to 1.98e8 < 2^31) and triggers split-K
+    x, xq, a_s, q, s, _ = problem(M, N, K, seed=M + N)
+    acc = w8a8_int32_accumulators(xq.cuda(), q.cuda())
+    ref_acc = O.w8a8_int32_accumulators(xq, q)
+    assert torch.equal(acc.cpu(), ref_acc)
+    y = apply_w8a8_linear(xq.cuda(), a_s.cuda(), q.cuda(), s.cuda(), out_dtype=torch.bfloat16)
+    assert torch.equal(bits(y.cpu()), bits(O.w8a8_native_epilogue(ref_acc, a_s, s, None, torch.bfloat16)))
+    assert device_status_ok()
+
+
+def test_saturated_inputs_reach_the_int32_extremes():
+    # all +-127 codes: every accumulator is +-K * 127^2, the largest magnitude the path can see
+    M, N, K = 130, 256, 12288
+    xq = torch.full((M, K), 127, dtype=torch.int8)
+    xq[::2] = -127
+    q = torch.full((N, K), 127, dtype=torch.int8)
+    q[1::2] = -127
+    for path in ("umma", "umma_swap"):
+        with forced_path(path):
+            acc = w8a8_int32_accumulators(xq.cuda(), q.cuda())
+        expect = (xq[:, :1].int() * q[:, :1].int().T) * K
+        assert torch.equal(acc.cpu(), expect), path
+
+
 def test_repeated_split_k_calls_leave_workspace_clean():
     # the split-K counters must return to zero: same call three times, same answer
     _, xq, a_s, q, s, _ = problem(48, 256, 8192, seed=9)
