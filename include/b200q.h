@@ -181,6 +181,42 @@ int b200q_tp_allreduce(void* const* peer_buffers, void* const* peer_flag_pads, i
                        size_t n_elems, int dtype, void* stream);
 
 /*
+ * Row-parallel linear for decode-sized batches with the sum over the tensor-parallel ranks
+ * fused into the GEMM kernel: replaces the pair "quantized linear, then dist.all_reduce(y)"
+ * of RowParallelLinear.forward (nanovllm/layers/linear.py:265-276) by ONE kernel per rank.
+ * Each CTA pushes its partial output tile (rounded to the output type, exactly what
+ * b200q_w8a8_gemm / b200q_w8a16_gemm would have stored) into every other rank's receive
+ * area with 8-byte peer stores over NVLink (two values and the call number per store, so
+ * no fence or separate flag is needed), polls (bounded) its own receive area for the same
+ * tile of the peers and stores the fp32 sum, taken in rank order, into y.  The result is
+ * bit-identical on every rank and bit-identical to the unfused decode kernel followed by
+ * b200q_tp_allreduce.
+ *
+ * peer_recv / peer_flags are HOST arrays of `world` DEVICE addresses as mapped into the
+ * calling process: rank r's receive area (recv_bytes bytes, 256-byte aligned; two halves
+ * used alternately, each must hold world * M * N * 4 bytes) and rank r's control words
+ * (B200Q_FUSED_FLAG_BYTES).  Both are zero-filled once before the first call and never
+ * touched by the caller afterwards.  y is an ordinary local tensor.  Every rank makes the
+ * same sequence of calls with the same M, N and dtype (K is the rank's share of the input
+ * features), ordered on one stream per rank.
+ * Limits: M <= B200Q_FUSED_MAX_M, N % 8 == 0, and the N / 8 CTAs of the kernel must be
+ * resident on the device at once; B200Q_ERR_UNSUPPORTED_SHAPE otherwise (nothing is
+ * launched and the caller takes the two-kernel route), B200Q_ERR_WORKSPACE when the
+ * receive area is too small.  A wait that runs out sets device status 0x601.
+ */
+#define B200Q_FUSED_MAX_M 64
+#define B200Q_FUSED_FLAG_BYTES 256u
+int b200q_w8a8_gemm_allreduce(const int8_t* xq, const float* a_scales, const int8_t* qweight,
+                              const float* w_scales, const void* bias, void* y, int M, int N,
+                              int K, int out_dtype, void* const* peer_recv,
+                              void* const* peer_flags, size_t recv_bytes, int rank, int world,
+                              void* stream);
+int b200q_w8a16_gemm_allreduce(const void* x, const int8_t* qweight, const float* scales,
+                               const void* bias, void* y, int M, int N, int K, int x_dtype,
+                               void* const* peer_recv, void* const* peer_flags,
+                               size_t recv_bytes, int rank, int world, void* stream);
+
+/*
  * W8A8 linear for callers that have no way to hand over scratch memory.
  * (No counterpart in the reference: its kernels never need scratch.)
  *

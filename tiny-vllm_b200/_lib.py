@@ -63,6 +63,14 @@ SIGNATURES = {
     "b200q_launch_count": (_c.c_uint64, []),
     "b200q_tp_allreduce": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_size_t,
                                       _c.c_int, _c.c_void_p]),
+    "b200q_w8a8_gemm_allreduce": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                             _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
+                                             _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_size_t,
+                                             _c.c_int, _c.c_int, _c.c_void_p]),
+    "b200q_w8a16_gemm_allreduce": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                              _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                              _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int,
+                                              _c.c_int, _c.c_void_p]),
     "b200q_w8a8_gemm_noalloc": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                            _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
                                            _c.c_int, _c.c_void_p]),

@@ -196,6 +196,70 @@ int b200q_w8a8_gemm(const int8_t* xq, const float* a_scales, const int8_t* qweig
   return run_w8a8(a);
 }
 
+int b200q_w8a8_gemm_allreduce(const int8_t* xq, const float* a_scales, const int8_t* qweight,
+                              const float* w_scales, const void* bias, void* y, int M, int N,
+                              int K, int out_dtype, void* const* peer_recv,
+                              void* const* peer_flags, size_t recv_bytes, int rank, int world,
+                              void* stream) {
+  if (xq == nullptr || a_scales == nullptr || qweight == nullptr || w_scales == nullptr ||
+      y == nullptr)
+    return B200Q_ERR_NULL_POINTER;
+  if (int rc = check_dims(M, N, K)) return rc;
+  if (out_dtype != B200Q_DTYPE_F16 && out_dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  if (!aligned16(xq) || !aligned16(qweight) || !aligned16(y) ||
+      (reinterpret_cast<uintptr_t>(a_scales) & 3u) != 0 ||
+      (reinterpret_cast<uintptr_t>(w_scales) & 3u) != 0 ||
+      (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 1u) != 0))
+    return B200Q_ERR_MISALIGNED;
+  DeviceInfo* d = device_info();
+  if (d == nullptr) return B200Q_ERR_LAUNCH;
+  if (d->cc_major != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+  GemmArgs a{};
+  a.x = xq;
+  a.w = qweight;
+  a.a_scales = a_scales;
+  a.w_scales = w_scales;
+  a.bias = bias;
+  a.y = y;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.dtype = out_dtype;
+  a.status = d->status_ptr;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return launch_w8a8_mma_decode_fused(a, peer_recv, peer_flags, recv_bytes, rank, world);
+}
+
+int b200q_w8a16_gemm_allreduce(const void* x, const int8_t* qweight, const float* scales,
+                               const void* bias, void* y, int M, int N, int K, int x_dtype,
+                               void* const* peer_recv, void* const* peer_flags,
+                               size_t recv_bytes, int rank, int world, void* stream) {
+  if (x == nullptr || qweight == nullptr || scales == nullptr || y == nullptr)
+    return B200Q_ERR_NULL_POINTER;
+  if (int rc = check_dims(M, N, K)) return rc;
+  if (x_dtype != B200Q_DTYPE_F16 && x_dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  if (!aligned16(x) || !aligned16(qweight) || !aligned16(y) ||
+      (reinterpret_cast<uintptr_t>(scales) & 3u) != 0 ||
+      (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 1u) != 0))
+    return B200Q_ERR_MISALIGNED;
+  DeviceInfo* d = device_info();
+  if (d == nullptr) return B200Q_ERR_LAUNCH;
+  if (d->cc_major != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+  GemmArgs a{};
+  a.x = x;
+  a.w = qweight;
+  a.w_scales = scales;
+  a.bias = bias;
+  a.y = y;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.dtype = x_dtype;
+  a.status = d->status_ptr;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return launch_w8a16_mma_decode_fused(a, peer_recv, peer_flags, recv_bytes, rank, world);
+}
+
 int b200q_w8a8_gemm_i32(const int8_t* xq, const int8_t* qweight, int32_t* acc, int M, int N, int K,
                         void* workspace, size_t workspace_bytes, void* stream) {
   if (xq == nullptr || qweight == nullptr || acc == nullptr) return B200Q_ERR_NULL_POINTER;

@@ -66,6 +66,11 @@ cudaError_t launch_w8a16_simt(const GemmArgs& a);
 bool mma_decode_applicable(int M);
 cudaError_t launch_w8a8_mma_decode(const GemmArgs& a);
 cudaError_t launch_w8a16_mma_decode(const GemmArgs& a);
+// The same kernels with the row-parallel sum over peer memory fused in; return B200Q_* codes.
+int launch_w8a8_mma_decode_fused(const GemmArgs& a, void* const* peer_recv,
+                                 void* const* peer_flags, size_t recv_bytes, int rank, int world);
+int launch_w8a16_mma_decode_fused(const GemmArgs& a, void* const* peer_recv,
+                                  void* const* peer_flags, size_t recv_bytes, int rank, int world);
 
 // gemm_umma.cu
 bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan);

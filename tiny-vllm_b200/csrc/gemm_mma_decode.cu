@@ -24,7 +24,10 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <type_traits>
+
 #include "common.h"
+#include "peer_sync.cuh"
 
 namespace b200q {
 namespace {
@@ -34,6 +37,128 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kChannels = 8;       // output channels per CTA (N side of the MMA)
 constexpr int kBlock = 64;         // K elements per block (one 16-byte load per lane)
 constexpr int kMaxMT = 4;          // up to 4 token tiles of 16 -> M <= 64
+
+// ---------------------------------------------------------------- fused all-reduce
+// Row-parallel layers (nanovllm/layers/linear.py:265-276) sum the ranks' partial results.
+// With FUSED kernels that sum happens inside the GEMM kernel, tile by tile, over peer
+// memory: CTA c of rank r rounds its partial tile to the output type (exactly what the
+// unfused kernel would store) and pushes it into slot r of every OTHER rank's receive area;
+// then it collects the same tile of every other rank from its own receive area, adds the
+// `world` partials in rank order in fp32 and stores the sum locally.  One NVLink trip, no
+// second kernel, and no fence or separate flag on the way: values travel as 8-byte words
+// {two 16-bit values, call number}; an aligned 8-byte store arrives whole, so a word whose
+// upper half equals the current call number is valid data.  The receiver polls the words
+// themselves (bounded).  Receive areas alternate between two halves by call parity, so a
+// rank that is one call ahead cannot overwrite words a slower rank still reads; being two
+// calls ahead is impossible because finishing a call needs every peer's words of that call.
+// Call numbers only grow (0 is skipped on wrap-around; the areas start zero-filled).
+struct FuseParams {
+  void* recv[8];        // every rank's receive area (both parity halves)
+  unsigned int* ctl[8]; // every rank's control words (only the own rank's are used)
+  size_t half_bytes;    // bytes of one parity half
+  int rank, world;
+};
+constexpr int kCtlEpoch = 0;    // calls completed by this rank
+constexpr int kCtlCounter = 1;  // CTAs of the running call that are done
+
+__device__ __forceinline__ void st_word8(void* p, uint32_t data, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(data), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_word8(const void* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
+// part: this CTA's tile in shared memory, [M][8] values of OutT.  All threads call.
+template <typename OutT>
+__device__ __forceinline__ void exchange_and_sum(const OutT* part, const FuseParams& fp, int M,
+                                                 int N, OutT* __restrict__ y, int* status) {
+  constexpr bool kBf16 = std::is_same<OutT, __nv_bfloat16>::value;
+  constexpr int kWordsPerTok = kChannels / 2;  // 8-byte words of one token row of the tile
+  __shared__ unsigned int s_epoch;
+  __shared__ int s_fail;
+  unsigned int* ctl = fp.ctl[fp.rank];
+  if (threadIdx.x == 0) {
+    unsigned int e = *reinterpret_cast<volatile unsigned int*>(ctl + kCtlEpoch) + 1u;
+    if (e == 0u) e = 1u;
+    s_epoch = e;
+    s_fail = 0;
+  }
+  __syncthreads();  // also publishes `part`
+  const unsigned int epoch = s_epoch;
+  const size_t half_off = (epoch & 1u) * fp.half_bytes;
+  const size_t slot_words = static_cast<size_t>(M) * (N / 2);  // one source rank's partial
+  const size_t tile_word0 = static_cast<size_t>(blockIdx.x) * kWordsPerTok;
+  const uint32_t* part_w = reinterpret_cast<const uint32_t*>(part);
+  const int words = M * kWordsPerTok;
+
+  // push: one 8-byte word {2 values, call number} per (peer, token, channel pair)
+  for (int i = threadIdx.x; i < words * fp.world; i += kThreads) {
+    const int peer = i / words, wi = i - peer * words;
+    if (peer == fp.rank) continue;  // the own tile is taken from shared memory below
+    const int tok = wi / kWordsPerTok, pair = wi - tok * kWordsPerTok;
+    uint2* dst = reinterpret_cast<uint2*>(static_cast<char*>(fp.recv[peer]) + half_off) +
+                 fp.rank * slot_words + static_cast<size_t>(tok) * (N / 2) + tile_word0 + pair;
+    st_word8(dst, part_w[wi], epoch);
+  }
+  // collect and sum in rank order
+  const uint2* mine =
+      reinterpret_cast<const uint2*>(static_cast<const char*>(fp.recv[fp.rank]) + half_off);
+  for (int wi = threadIdx.x; wi < words; wi += kThreads) {
+    const int tok = wi / kWordsPerTok, pair = wi - tok * kWordsPerTok;
+    const size_t off = static_cast<size_t>(tok) * (N / 2) + tile_word0 + pair;
+    float lo = 0.f, hi = 0.f;
+    bool ok = true;
+    for (int r = 0; r < fp.world; ++r) {
+      uint32_t w;
+      if (r == fp.rank) {
+        w = part_w[wi];
+      } else {
+        const uint2* src = mine + r * slot_words + off;
+        uint2 v = ld_word8(src);
+        if (v.y != epoch) {
+          const long long t0 = clock64();
+          do {
+            v = ld_word8(src);
+          } while (v.y != epoch && clock64() - t0 < kSpinLimitCycles);
+          if (v.y != epoch) ok = false;
+        }
+        w = v.x;
+      }
+      if (kBf16) {
+        lo += __uint_as_float(w << 16);
+        hi += __uint_as_float(w & 0xFFFF0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        lo += f.x;
+        hi += f.y;
+      }
+    }
+    if (ok) {
+      uint32_t out;
+      if (kBf16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        out = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        out = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      reinterpret_cast<uint32_t*>(y)[static_cast<size_t>(tok) * (N / 2) + tile_word0 + pair] = out;
+    } else {
+      s_fail = 1;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_fail != 0) atomicCAS(status, 0, 0x601);
+    // the last CTA of the call advances the rank's call number (the next launch reads it)
+    if (atomicAdd(ctl + kCtlCounter, 1u) == gridDim.x - 1) {
+      ctl[kCtlCounter] = 0u;
+      *reinterpret_cast<volatile unsigned int*>(ctl + kCtlEpoch) = epoch;
+    }
+  }
+}
 
 template <typename T>
 __device__ __forceinline__ T from_float(float v);
@@ -120,12 +245,14 @@ __device__ __forceinline__ uint2 expand4<__nv_bfloat16>(uint32_t w) {
 // MT = number of 16-token tiles.  Lane (g = lane / 4, t = lane % 4): weight row g of the
 // CTA's 8 channels, bytes [16 t, 16 t + 16) of each 64-byte K block; the same byte range
 // of token rows g and g + 8 of every token tile.
-template <typename OutT, int MT, bool RAW_I32>
+template <typename OutT, int MT, bool RAW_I32, bool FUSED>
 __global__ void __launch_bounds__(kThreads)
 w8a8_mma_decode_kernel(const int8_t* __restrict__ xq, const int8_t* __restrict__ w,
                        const float* __restrict__ a_s, const float* __restrict__ w_s,
-                       const OutT* __restrict__ bias, void* __restrict__ out, int M, int N, int K) {
+                       const OutT* __restrict__ bias, void* __restrict__ out, int M, int N, int K,
+                       const FuseParams fp, int* status) {
   __shared__ int red[kWarps][MT * 16 * kChannels];
+  __shared__ __align__(16) OutT part[FUSED ? MT * 16 * kChannels : 8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int ch = blockIdx.x * kChannels + g;
@@ -194,20 +321,26 @@ w8a8_mma_decode_kernel(const int8_t* __restrict__ xq, const int8_t* __restrict__
     } else {
       const float b = bias != nullptr ? to_float<OutT>(bias[n]) : 0.f;
       const float v = __fadd_rn(__fmul_rn(__fmul_rn(static_cast<float>(sum), a_s[tok]), w_s[n]), b);
-      reinterpret_cast<OutT*>(out)[idx] = from_float<OutT>(v);
+      if (FUSED) {
+        part[o] = from_float<OutT>(v);
+      } else {
+        reinterpret_cast<OutT*>(out)[idx] = from_float<OutT>(v);
+      }
     }
   }
+  if (FUSED) exchange_and_sum<OutT>(part, fp, M, N, reinterpret_cast<OutT*>(out), status);
 }
 
 // ------------------------------------------------------------------------ W8A16
 // Same ownership; a 64-element K block is four k16 steps, lane t supplies physical
 // k [16 t + 4 j, 16 t + 4 j + 4) to step j (4 weights = one word, 4 activations = 8 bytes).
-template <typename T, int MT>
+template <typename T, int MT, bool FUSED>
 __global__ void __launch_bounds__(kThreads)
 w8a16_mma_decode_kernel(const T* __restrict__ x, const int8_t* __restrict__ w,
                         const float* __restrict__ s, const T* __restrict__ bias,
-                        T* __restrict__ y, int M, int N, int K) {
+                        T* __restrict__ y, int M, int N, int K, const FuseParams fp, int* status) {
   __shared__ float red[kWarps][MT * 16 * kChannels];
+  __shared__ __align__(16) T part[FUSED ? MT * 16 * kChannels : 8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int ch = blockIdx.x * kChannels + g;
@@ -272,19 +405,41 @@ w8a16_mma_decode_kernel(const T* __restrict__ x, const int8_t* __restrict__ w,
 #pragma unroll
     for (int wi = 0; wi < kWarps; ++wi) sum = __fadd_rn(sum, red[wi][o]);  // fixed order
     const float b = bias != nullptr ? to_float<T>(bias[n]) : 0.f;
-    y[static_cast<size_t>(tok) * N + n] = from_float<T>(__fadd_rn(__fmul_rn(sum, s[n]), b));
+    const T v = from_float<T>(__fadd_rn(__fmul_rn(sum, s[n]), b));
+    if (FUSED) {
+      part[o] = v;
+    } else {
+      y[static_cast<size_t>(tok) * N + n] = v;
+    }
   }
+  if (FUSED) exchange_and_sum<T>(part, fp, M, N, y, status);
 }
 
-template <typename OutT, bool RAW>
-void launch_a8(const GemmArgs& a, int mt) {
+// CTAs of a fused kernel wait for the same CTA of the peers, so every CTA of the grid has to
+// be resident at once: the launch is refused (the caller then takes the two-kernel route)
+// when the grid exceeds what the device holds.
+thread_local bool g_fused_refused = false;
+template <typename Kernel>
+bool all_ctas_resident(Kernel kernel, int grid) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess)
+    return false;
+  return static_cast<long long>(grid) <= static_cast<long long>(per_sm) * sm_count();
+}
+
+template <typename OutT, bool RAW, bool FUSED = false>
+void launch_a8(const GemmArgs& a, int mt, const FuseParams& fp = FuseParams{}) {
   const int grid = (a.N + kChannels - 1) / kChannels;
   const int8_t* xq = reinterpret_cast<const int8_t*>(a.x);
   const OutT* bias = reinterpret_cast<const OutT*>(a.bias);
   void* out = RAW ? static_cast<void*>(a.acc_out) : a.y;
 #define B200Q_LAUNCH_A8(MT)                                                                  \
-  w8a8_mma_decode_kernel<OutT, MT, RAW><<<grid, kThreads, 0, a.stream>>>(                     \
-      xq, a.w, a.a_scales, a.w_scales, bias, out, a.M, a.N, a.K)
+  if (FUSED && !all_ctas_resident(w8a8_mma_decode_kernel<OutT, MT, RAW, FUSED>, grid)) {      \
+    g_fused_refused = true;                                                                  \
+    return;                                                                                  \
+  }                                                                                          \
+  w8a8_mma_decode_kernel<OutT, MT, RAW, FUSED><<<grid, kThreads, 0, a.stream>>>(              \
+      xq, a.w, a.a_scales, a.w_scales, bias, out, a.M, a.N, a.K, fp, a.status)
   switch (mt) {
     case 1: B200Q_LAUNCH_A8(1); break;
     case 2: B200Q_LAUNCH_A8(2); break;
@@ -294,13 +449,17 @@ void launch_a8(const GemmArgs& a, int mt) {
 #undef B200Q_LAUNCH_A8
 }
 
-template <typename T>
-void launch_a16(const GemmArgs& a, int mt) {
+template <typename T, bool FUSED = false>
+void launch_a16(const GemmArgs& a, int mt, const FuseParams& fp = FuseParams{}) {
   const int grid = (a.N + kChannels - 1) / kChannels;
 #define B200Q_LAUNCH_A16(MT)                                                                 \
-  w8a16_mma_decode_kernel<T, MT><<<grid, kThreads, 0, a.stream>>>(                            \
+  if (FUSED && !all_ctas_resident(w8a16_mma_decode_kernel<T, MT, FUSED>, grid)) {             \
+    g_fused_refused = true;                                                                  \
+    return;                                                                                  \
+  }                                                                                          \
+  w8a16_mma_decode_kernel<T, MT, FUSED><<<grid, kThreads, 0, a.stream>>>(                     \
       reinterpret_cast<const T*>(a.x), a.w, a.w_scales, reinterpret_cast<const T*>(a.bias),   \
-      reinterpret_cast<T*>(a.y), a.M, a.N, a.K)
+      reinterpret_cast<T*>(a.y), a.M, a.N, a.K, fp, a.status)
   switch (mt) {
     case 1: B200Q_LAUNCH_A16(1); break;
     case 2: B200Q_LAUNCH_A16(2); break;
@@ -340,6 +499,70 @@ cudaError_t launch_w8a16_mma_decode(const GemmArgs& a) {
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) count_launch();
   return e;
+}
+
+// Fills the exchange parameters; returns a B200Q_* code.
+static int make_fuse_params(const GemmArgs& a, void* const* peer_recv, void* const* peer_flags,
+                            size_t recv_bytes, int rank, int world, FuseParams* fp) {
+  if (peer_recv == nullptr || peer_flags == nullptr) return B200Q_ERR_NULL_POINTER;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return B200Q_ERR_BAD_ARGUMENT;
+  if (a.M > B200Q_FUSED_MAX_M || (a.N % kChannels) != 0) return B200Q_ERR_UNSUPPORTED_SHAPE;
+  const size_t half = (recv_bytes / 2) & ~static_cast<size_t>(255);
+  // 4 bytes per value on the wire: 16 bits of data and its share of the call number
+  if (static_cast<size_t>(world) * a.M * a.N * 4 > half) return B200Q_ERR_WORKSPACE;
+  for (int r = 0; r < world; ++r) {
+    if (peer_recv[r] == nullptr || peer_flags[r] == nullptr) return B200Q_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(peer_recv[r]) & 255u) != 0 ||
+        (reinterpret_cast<uintptr_t>(peer_flags[r]) & 15u) != 0)
+      return B200Q_ERR_MISALIGNED;
+    fp->recv[r] = peer_recv[r];
+    fp->ctl[r] = static_cast<unsigned int*>(peer_flags[r]);
+  }
+  fp->half_bytes = half;
+  fp->rank = rank;
+  fp->world = world;
+  return B200Q_OK;
+}
+
+static int finish_fused_launch() {
+  if (g_fused_refused) {
+    g_fused_refused = false;
+    return B200Q_ERR_UNSUPPORTED_SHAPE;
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  count_launch();
+  return B200Q_OK;
+}
+
+int launch_w8a8_mma_decode_fused(const GemmArgs& a, void* const* peer_recv,
+                                 void* const* peer_flags, size_t recv_bytes, int rank, int world) {
+  FuseParams fp{};
+  if (int rc = make_fuse_params(a, peer_recv, peer_flags, recv_bytes, rank, world, &fp)) return rc;
+  const int mt = (a.M + 15) / 16;
+  if (a.dtype == B200Q_DTYPE_BF16) {
+    launch_a8<__nv_bfloat16, false, true>(a, mt, fp);
+  } else {
+    launch_a8<__half, false, true>(a, mt, fp);
+  }
+  return finish_fused_launch();
+}
+
+int launch_w8a16_mma_decode_fused(const GemmArgs& a, void* const* peer_recv,
+                                  void* const* peer_flags, size_t recv_bytes, int rank,
+                                  int world) {
+  FuseParams fp{};
+  if (int rc = make_fuse_params(a, peer_recv, peer_flags, recv_bytes, rank, world, &fp)) return rc;
+  const int mt = (a.M + 15) / 16;
+  if (a.dtype == B200Q_DTYPE_BF16) {
+    launch_a16<__nv_bfloat16, true>(a, mt, fp);
+  } else {
+    launch_a16<__half, true>(a, mt, fp);
+  }
+  return finish_fused_launch();
 }
 
 }  // namespace b200q

@@ -19,6 +19,7 @@
 #include <cuda_runtime.h>
 
 #include "common.h"
+#include "peer_sync.cuh"
 
 namespace b200q {
 namespace {
@@ -30,7 +31,6 @@ constexpr int kSlotEpoch = 0;     // number of completed calls
 constexpr int kSlotCounter = 1;   // CTAs of this rank that finished the reduce phase
 constexpr int kSlotA = 16;        // [kSlotA + src]: src's input is ready (epoch)
 constexpr int kSlotB = 32;        // [kSlotB + src]: src's writes are done (epoch)
-constexpr long long kSpinLimitCycles = 2000000000LL;  // about one second
 
 struct Params {
   void* buf[kMaxWorld];
@@ -40,71 +40,6 @@ struct Params {
   int is_bf16;
   int* status;
 };
-
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_peer16(const void* p) {
-  uint4 v;
-  // weak load, not cached in L1: each address is read once per call and the call's first
-  // barrier orders it after the peers' writes
-  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_peer16(void* p, const uint4 v) {
-  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
-
-// Waits until the flag holds at least `epoch` (wrap-safe).  False when the limit ran out.
-__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int epoch) {
-  const long long t0 = clock64();
-  while (static_cast<int>(ld_acquire_sys(flag) - epoch) < 0) {
-    if (clock64() - t0 > kSpinLimitCycles) return false;
-  }
-  return true;
-}
-
-template <bool BF16>
-__device__ __forceinline__ void accumulate(float (&acc)[8], const uint4 v) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f;
-    if (BF16) {
-      f = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
-    } else {
-      f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-    }
-    acc[2 * i] += f.x;
-    acc[2 * i + 1] += f.y;
-  }
-}
-
-template <bool BF16>
-__device__ __forceinline__ uint4 pack(const float (&acc)[8]) {
-  uint32_t w[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (BF16) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-      w[i] = *reinterpret_cast<const uint32_t*>(&h);
-    } else {
-      const __half2 h = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
-      w[i] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-  }
-  return make_uint4(w[0], w[1], w[2], w[3]);
-}
 
 // W = compile-time bound on the number of ranks, U = chunks per thread per iteration: all
 // U * world loads of an iteration are issued before the first use, so that enough bytes are

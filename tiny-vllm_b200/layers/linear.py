@@ -264,14 +264,19 @@ class RowParallelLinear(LinearBase):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         bias = self.bias if self.tp_rank == 0 else None
+        comm = _peer_all_reduce if self.tp_size > 1 else None
         if self.quant_method is None:
             y = F.linear(x, self.weight, bias)
         else:
+            if comm is not None and x.is_cuda and hasattr(comm, "fused_fits"):
+                # decode-sized batch: GEMM and the sum over ranks in one kernel
+                fused = self.quant_method.apply_row_parallel(x, self, bias, comm)
+                if fused is not None:
+                    return fused
             # As in the reference (linear.py:270-271 with int8.py:29 / w8a8.py:37): a
             # ``None`` bias lets the quant method pick ``self.bias`` on every rank.
             y = self.quant_method.apply(x, self, bias)
         if self.tp_size > 1:
-            comm = _peer_all_reduce
             if comm is not None and y.is_cuda and y.numel() % 8 == 0 \
                     and y.numel() * y.element_size() <= comm.slot_bytes:
                 shared = comm.buffer(y.shape, y.dtype)

@@ -13,6 +13,12 @@ Usage (every rank, same order of calls)::
     y = comm.buffer((tokens, hidden), torch.bfloat16)  # write the partial result here
     ...                                                # e.g. the GEMM's output pointer
     comm.all_reduce_(y)                                # y now holds the sum on every rank
+
+For decode-sized batches (at most 64 tokens) the sum can be fused into the GEMM kernel
+itself (``b200q_w8a8_gemm_allreduce`` / ``b200q_w8a16_gemm_allreduce``): every CTA pushes
+its partial tile to all ranks and adds up the peers' tiles, so a row-parallel layer is one
+kernel.  ``fused_w8a8`` / ``fused_w8a16`` return ``None`` when the library refuses the shape
+and the caller then uses the two-kernel route.
 """
 from __future__ import annotations
 
@@ -25,12 +31,14 @@ from .. import _lib
 
 _DTYPE_IDS = {torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16}
 _PAD_BYTES = 4096
+_FUSED_MAX_M = 64
+_FUSED_FLAG_BYTES = 256
 
 
 class PeerAllReduce:
     """Owns one symmetric data buffer and one symmetric flag pad for a process group."""
 
-    def __init__(self, max_bytes: int, group=None, slots: int = 2):
+    def __init__(self, max_bytes: int, group=None, slots: int = 2, fused_bytes: int = 16 << 20):
         import torch.distributed._symmetric_memory as symm_mem
 
         if not dist.is_initialized():
@@ -50,11 +58,22 @@ class PeerAllReduce:
         self._pad = symm_mem.empty(_PAD_BYTES, dtype=torch.uint8, device=dev)
         self._pad.zero_()
         self._pad_hdl = symm_mem.rendezvous(self._pad, name)
+        # receive area and flags of the fused decode kernels
+        self.fused_bytes = (fused_bytes + 511) // 512 * 512
+        self._recv = symm_mem.empty(self.fused_bytes, dtype=torch.uint8, device=dev)
+        self._recv.zero_()
+        self._recv_hdl = symm_mem.rendezvous(self._recv, name)
+        self._fflags = symm_mem.empty(_FUSED_FLAG_BYTES, dtype=torch.uint8, device=dev)
+        self._fflags.zero_()
+        self._fflags_hdl = symm_mem.rendezvous(self._fflags, name)
         torch.cuda.synchronize()
         dist.barrier(self.group)           # every pad is zero before anyone signals
         self._data_ptrs = [int(p) for p in self._data_hdl.buffer_ptrs]
         pads = [int(p) for p in self._pad_hdl.buffer_ptrs]
         self._pad_arr = (ctypes.c_void_p * self.world)(*pads)
+        self._recv_arr = (ctypes.c_void_p * self.world)(*[int(p) for p in self._recv_hdl.buffer_ptrs])
+        self._fflags_arr = (ctypes.c_void_p * self.world)(
+            *[int(p) for p in self._fflags_hdl.buffer_ptrs])
 
     def buffer(self, shape, dtype: torch.dtype) -> torch.Tensor:
         """A tensor inside the symmetric allocation (slots are handed out round-robin, so a
@@ -87,3 +106,43 @@ class PeerAllReduce:
                                            torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "b200q_tp_allreduce", f"n={t.numel()} world={self.world}")
         return t
+
+    # ------------------------------------------------------------------ fused decode route
+    def fused_fits(self, tokens: int, n_out: int) -> bool:
+        return (0 < tokens <= _FUSED_MAX_M and n_out % 8 == 0
+                and self.world * tokens * n_out * 4 <= self.fused_bytes // 2)
+
+    def _finish_fused(self, rc: int, name: str, detail: str, y: torch.Tensor):
+        if rc == _lib.ERR_UNSUPPORTED_SHAPE:
+            return None
+        _lib.check(rc, name, detail)
+        return y
+
+    def fused_w8a8(self, x_q, a_scales, qweight, w_scales, bias, out_dtype):
+        """Row-parallel W8A8 linear plus the sum over ranks in one kernel.  ``x_q`` int8
+        ``[M, K_local]``, ``qweight`` int8 ``[N, K_local]``; returns ``[M, N]`` or ``None``."""
+        M, K = x_q.shape
+        N = qweight.shape[0]
+        if not self.fused_fits(M, N):
+            return None
+        y = torch.empty((M, N), dtype=out_dtype, device=x_q.device)
+        rc = _lib.lib().b200q_w8a8_gemm_allreduce(
+            x_q.data_ptr(), a_scales.data_ptr(), qweight.data_ptr(), w_scales.data_ptr(),
+            None if bias is None else bias.data_ptr(), y.data_ptr(), M, N, K,
+            _DTYPE_IDS[out_dtype], self._recv_arr, self._fflags_arr, self.fused_bytes,
+            self.rank, self.world, torch.cuda.current_stream().cuda_stream)
+        return self._finish_fused(rc, "b200q_w8a8_gemm_allreduce", f"M={M} N={N} K={K}", y)
+
+    def fused_w8a16(self, x_2d, qweight, scales, bias):
+        """Row-parallel W8A16 linear plus the sum over ranks in one kernel."""
+        M, K = x_2d.shape
+        N = qweight.shape[0]
+        if not self.fused_fits(M, N):
+            return None
+        y = torch.empty((M, N), dtype=x_2d.dtype, device=x_2d.device)
+        rc = _lib.lib().b200q_w8a16_gemm_allreduce(
+            x_2d.data_ptr(), qweight.data_ptr(), scales.data_ptr(),
+            None if bias is None else bias.data_ptr(), y.data_ptr(), M, N, K,
+            _DTYPE_IDS[x_2d.dtype], self._recv_arr, self._fflags_arr, self.fused_bytes,
+            self.rank, self.world, torch.cuda.current_stream().cuda_stream)
+        return self._finish_fused(rc, "b200q_w8a16_gemm_allreduce", f"M={M} N={N} K={K}", y)

@@ -28,6 +28,13 @@ class QuantMethod(abc.ABC):
     def quantize_activation(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor] | None:
         """Returns ``(x_q, a_scales)`` or ``None`` when activations stay in 16 bit."""
 
+    def apply_row_parallel(self, x: torch.Tensor, layer: nn.Module, bias, comm):
+        """Optional: the linear and the sum over tensor-parallel ranks in one kernel, through
+        ``comm`` (``layers.tp_comm.PeerAllReduce``).  ``None`` = not available for this call;
+        the layer then runs ``apply`` followed by an all-reduce.  (No counterpart in the
+        reference, which always runs the two steps: ``nanovllm/layers/linear.py:265-276``.)"""
+        return None
+
 
 def frozen(shape: tuple[int, ...], dtype: torch.dtype) -> nn.Parameter:
     """An uninitialised parameter that takes no gradient."""

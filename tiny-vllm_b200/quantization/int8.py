@@ -26,3 +26,15 @@ class Int8WeightOnlyQuantMethod(QuantMethod):
               bias: torch.Tensor | None = None) -> torch.Tensor:
         chosen_bias = bias if bias is not None else layer.bias
         return apply_int8_weight_only_linear(x, layer.qweight, layer.scales, chosen_bias)
+
+    def apply_row_parallel(self, x: torch.Tensor, layer: nn.Module, bias, comm):
+        """Multiply and sum over the tensor-parallel ranks in one GEMM kernel (decode-sized
+        batches); ``None`` when the fused kernel does not take the shape."""
+        n_out = layer.qweight.shape[0]
+        tokens = x.numel() // x.shape[-1]
+        if not comm.fused_fits(tokens, n_out) or x.dtype not in (torch.float16, torch.bfloat16):
+            return None
+        chosen = bias if bias is not None else layer.bias
+        x_2d = x.contiguous().view(-1, x.shape[-1])
+        y = comm.fused_w8a16(x_2d, layer.qweight, layer.scales, chosen)
+        return None if y is None else y.view(*x.shape[:-1], n_out)

@@ -34,3 +34,15 @@ class W8A8QuantMethod(QuantMethod):
             out_dtype=x.dtype,
             out_shape=(*x.shape[:-1], n_out),
         )
+
+    def apply_row_parallel(self, x: torch.Tensor, layer: nn.Module, bias, comm):
+        """Quantise, multiply and sum over the tensor-parallel ranks in one GEMM kernel
+        (decode-sized batches); ``None`` when the fused kernel does not take the shape."""
+        n_out = layer.qweight.shape[0]
+        tokens = x.numel() // x.shape[-1]
+        if not comm.fused_fits(tokens, n_out):
+            return None
+        x_q, a_scales = self.quantize_activation(x)
+        chosen = layer.bias if bias is None else bias
+        y = comm.fused_w8a8(x_q, a_scales, layer.qweight, layer.w_scales, chosen, x.dtype)
+        return None if y is None else y.view(*x.shape[:-1], n_out)
