@@ -217,6 +217,23 @@ int b200q_w8a16_gemm_allreduce(const void* x, const int8_t* qweight, const float
                                size_t recv_bytes, int rank, int world, void* stream);
 
 /*
+ * Sum all-reduce of a SMALL 16-bit tensor over the tensor-parallel ranks in one NVLink trip
+ * (same use as b200q_tp_allreduce, nanovllm/layers/linear.py:274-275, for tensors up to a
+ * few hundred kilobytes, where two flag barriers cost more than the data).  x and y are
+ * ordinary local tensors of n_elems values (y may be x); every rank pushes x to every peer
+ * as 8-byte words tagged with the call number and sums what it receives in rank order
+ * (fp32), so all ranks get bit-identical results, equal to those of b200q_tp_allreduce.
+ * peer_recv / peer_flags / recv_bytes are the receive areas and control words of the
+ * fused kernels above (shared call numbering: calls of the three entry points may be
+ * mixed freely as long as every rank makes the same sequence); each half of the receive
+ * area must hold world * n_elems * 4 bytes, else B200Q_ERR_WORKSPACE.  n_elems % 8 == 0.
+ * A wait that runs out sets device status 0x602.
+ */
+int b200q_tp_allreduce_small(const void* x, void* y, size_t n_elems, int dtype,
+                             void* const* peer_recv, void* const* peer_flags,
+                             size_t recv_bytes, int rank, int world, void* stream);
+
+/*
  * W8A8 linear for callers that have no way to hand over scratch memory.
  * (No counterpart in the reference: its kernels never need scratch.)
  *

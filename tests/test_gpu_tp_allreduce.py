@@ -55,6 +55,37 @@ def _worker(rank, world, port, out_dir):
             ok = ok and same
             if not same:
                 notes.append(f"call {call}: mismatch, max diff {(t.cpu().float() - expect.float()).abs().max()}")
+        # one-trip kernel for small tensors: any local tensor, in place, same bits
+        for call, (n, dtype) in enumerate([(8, torch.bfloat16), (4096, torch.float16),
+                                           (16 * 1024, torch.bfloat16), (96 * 1024, torch.bfloat16),
+                                           (512 * 1024, torch.bfloat16), (8, torch.float16)]):
+            parts = [_rank_tensor(r, n, 50 + call, dtype) for r in range(world)]
+            expect = torch.zeros(n, dtype=torch.float32)
+            for r in range(world):
+                expect += parts[r].float()
+            expect = expect.to(dtype)
+            t = parts[rank].cuda()
+            if world * n * 4 > comm.fused_bytes // 2:
+                continue
+            comm.all_reduce_small_(t)
+            torch.cuda.synchronize()
+            if not torch.equal(t.cpu().view(torch.int16), expect.view(torch.int16)):
+                ok = False
+                notes.append(f"one-trip call {call} (n={n}): mismatch")
+        ok = ok and _lib.lib().b200q_device_status() == 0
+        # latency by size: one-trip vs two-shot vs NCCL (CUDA-graph replays)
+        for n in (16 * 1024, 128 * 1024, 512 * 1024, 1024 * 1024):
+            if world * n * 4 > comm.fused_bytes // 2:
+                continue
+            loc = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+            sym = comm.buffer((n,), torch.bfloat16)
+            sym.zero_()
+            row = [f"{n * 2 // 1024} KiB:"]
+            for fn, name in ((lambda: comm.all_reduce_small_(loc), "one-trip"),
+                             (lambda: comm.all_reduce_(sym), "two-shot"),
+                             (lambda: dist.all_reduce(loc), "nccl")):
+                row.append(f"{name} {_graph_time_us(fn):.1f} us")
+            notes.append(" ".join(row))
         ok = ok and _lib.lib().b200q_device_status() == 0
         # timing against NCCL on the largest message
         t = comm.buffer((8192 * 1024,), torch.bfloat16)

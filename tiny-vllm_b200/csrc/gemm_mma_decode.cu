@@ -58,17 +58,7 @@ struct FuseParams {
   size_t half_bytes;    // bytes of one parity half
   int rank, world;
 };
-constexpr int kCtlEpoch = 0;    // calls completed by this rank
-constexpr int kCtlCounter = 1;  // CTAs of the running call that are done
 
-__device__ __forceinline__ void st_word8(void* p, uint32_t data, uint32_t tag) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(data), "r"(tag) : "memory");
-}
-__device__ __forceinline__ uint2 ld_word8(const void* p) {
-  uint2 v;
-  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
-}
 
 // part: this CTA's tile in shared memory, [M][8] values of OutT.  All threads call.
 template <typename OutT>
@@ -80,9 +70,7 @@ __device__ __forceinline__ void exchange_and_sum(const OutT* part, const FusePar
   __shared__ int s_fail;
   unsigned int* ctl = fp.ctl[fp.rank];
   if (threadIdx.x == 0) {
-    unsigned int e = *reinterpret_cast<volatile unsigned int*>(ctl + kCtlEpoch) + 1u;
-    if (e == 0u) e = 1u;
-    s_epoch = e;
+    s_epoch = next_epoch(ctl);
     s_fail = 0;
   }
   __syncthreads();  // also publishes `part`
@@ -115,16 +103,7 @@ __device__ __forceinline__ void exchange_and_sum(const OutT* part, const FusePar
       if (r == fp.rank) {
         w = part_w[wi];
       } else {
-        const uint2* src = mine + r * slot_words + off;
-        uint2 v = ld_word8(src);
-        if (v.y != epoch) {
-          const long long t0 = clock64();
-          do {
-            v = ld_word8(src);
-          } while (v.y != epoch && clock64() - t0 < kSpinLimitCycles);
-          if (v.y != epoch) ok = false;
-        }
-        w = v.x;
+        if (!wait_word8(mine + r * slot_words + off, epoch, &w)) ok = false;
       }
       if (kBf16) {
         lo += __uint_as_float(w << 16);
@@ -152,11 +131,7 @@ __device__ __forceinline__ void exchange_and_sum(const OutT* part, const FusePar
   __syncthreads();
   if (threadIdx.x == 0) {
     if (s_fail != 0) atomicCAS(status, 0, 0x601);
-    // the last CTA of the call advances the rank's call number (the next launch reads it)
-    if (atomicAdd(ctl + kCtlCounter, 1u) == gridDim.x - 1) {
-      ctl[kCtlCounter] = 0u;
-      *reinterpret_cast<volatile unsigned int*>(ctl + kCtlEpoch) = epoch;
-    }
+    finish_call(ctl, epoch);
   }
 }
 

@@ -87,4 +87,45 @@ __device__ __forceinline__ uint4 pack(const float (&acc)[8]) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+
+// ---- tagged words: the exchange format of the one-trip kernels (fused decode GEMM +
+// all-reduce, small all-reduce).  A value pair travels as an aligned 8-byte word {data,
+// call number}; such a store arrives whole, so a word whose tag equals the current call
+// number is valid data and no fence or separate flag is needed.
+constexpr int kCtlEpoch = 0;    // control word: calls completed by this rank
+constexpr int kCtlCounter = 1;  // control word: CTAs of the running call that are done
+
+__device__ __forceinline__ void st_word8(void* p, uint32_t data, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(data), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_word8(const void* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+// Polls a tagged word until it carries `epoch`; false when the limit ran out.
+__device__ __forceinline__ bool wait_word8(const void* p, uint32_t epoch, uint32_t* data) {
+  uint2 v = ld_word8(p);
+  if (v.y != epoch) {
+    const long long t0 = clock64();
+    do {
+      v = ld_word8(p);
+    } while (v.y != epoch && clock64() - t0 < kSpinLimitCycles);
+  }
+  *data = v.x;
+  return v.y == epoch;
+}
+// The call number of the launch that is starting (0 is never used as a tag).
+__device__ __forceinline__ unsigned int next_epoch(const unsigned int* ctl) {
+  unsigned int e = *reinterpret_cast<const volatile unsigned int*>(ctl + kCtlEpoch) + 1u;
+  return e == 0u ? 1u : e;
+}
+// Called by one thread per CTA at the end: the last CTA publishes the finished call number.
+__device__ __forceinline__ void finish_call(unsigned int* ctl, unsigned int epoch) {
+  if (atomicAdd(ctl + kCtlCounter, 1u) == gridDim.x - 1) {
+    ctl[kCtlCounter] = 0u;
+    *reinterpret_cast<volatile unsigned int*>(ctl + kCtlEpoch) = epoch;
+  }
+}
+
 }  // namespace b200q

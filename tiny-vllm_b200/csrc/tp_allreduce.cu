@@ -126,6 +126,81 @@ tp_allreduce_kernel(const Params p) {
   }
 }
 
+// ---------------------------------------------------------------- small tensors, one trip
+// For tensors of up to a few hundred kilobytes the two barriers above cost more than the
+// data.  Here every rank pushes its whole tensor to every peer as tagged 8-byte words and
+// then sums what it received, in rank order: one NVLink trip, no fence, no flag.  Shares
+// the receive area, the parity halves and the call numbering with the fused decode kernels
+// (the same argument shows that no rank overwrites words a peer still reads).  x and y are
+// ordinary local tensors (y may be x).  CTA c of every rank handles the same chunk range,
+// and all CTAs are resident, so no CTA waits for one that cannot run.
+struct OneTripParams {
+  void* recv[kMaxWorld];
+  unsigned int* ctl;   // this rank's control words
+  size_t half_bytes;
+  const uint4* x;
+  uint4* y;
+  unsigned long long n_chunks;
+  int rank, world;
+  int* status;
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads)
+tp_allreduce_onetrip_kernel(const OneTripParams p) {
+  __shared__ unsigned int s_epoch;
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) {
+    s_epoch = next_epoch(p.ctl);
+    s_fail = 0;
+  }
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
+  const size_t half_off = (epoch & 1u) * p.half_bytes;
+  const unsigned long long slot_words = p.n_chunks * 4;
+  const unsigned long long first = static_cast<unsigned long long>(blockIdx.x) * kThreads + threadIdx.x;
+  const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * kThreads;
+
+  for (unsigned long long c = first; c < p.n_chunks; c += stride) {
+    const uint4 v = p.x[c];
+    for (int peer = 0; peer < p.world; ++peer) {
+      if (peer == p.rank) continue;
+      uint2* dst = reinterpret_cast<uint2*>(static_cast<char*>(p.recv[peer]) + half_off) +
+                   p.rank * slot_words + c * 4;
+      st_word8(dst + 0, v.x, epoch);
+      st_word8(dst + 1, v.y, epoch);
+      st_word8(dst + 2, v.z, epoch);
+      st_word8(dst + 3, v.w, epoch);
+    }
+  }
+  const uint2* mine = reinterpret_cast<const uint2*>(static_cast<const char*>(p.recv[p.rank]) + half_off);
+  bool ok = true;
+  for (unsigned long long c = first; c < p.n_chunks; c += stride) {
+    const uint4 own = p.x[c];
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int r = 0; r < p.world; ++r) {
+      uint4 v = own;
+      if (r != p.rank) {
+        const uint2* src = mine + r * slot_words + c * 4;
+        ok &= wait_word8(src + 0, epoch, &v.x);
+        ok &= wait_word8(src + 1, epoch, &v.y);
+        ok &= wait_word8(src + 2, epoch, &v.z);
+        ok &= wait_word8(src + 3, epoch, &v.w);
+      }
+      accumulate<BF16>(acc, v);
+    }
+    if (ok) p.y[c] = pack<BF16>(acc);
+  }
+  if (!ok) s_fail = 1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_fail != 0) atomicCAS(p.status, 0, 0x602);
+    finish_call(p.ctl, epoch);
+  }
+}
+
 }  // namespace
 }  // namespace b200q
 
@@ -167,6 +242,53 @@ extern "C" int b200q_tp_allreduce(void* const* peer_buffers, void* const* peer_f
     else B200Q_AR_LAUNCH(false, 8, 1);
   }
 #undef B200Q_AR_LAUNCH
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  count_launch();
+  return B200Q_OK;
+}
+
+extern "C" int b200q_tp_allreduce_small(const void* x, void* y, size_t n_elems, int dtype,
+                                        void* const* peer_recv, void* const* peer_flags,
+                                        size_t recv_bytes, int rank, int world, void* stream) {
+  using namespace b200q;
+  if (x == nullptr || y == nullptr || peer_recv == nullptr || peer_flags == nullptr)
+    return B200Q_ERR_NULL_POINTER;
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return B200Q_ERR_BAD_ARGUMENT;
+  if (dtype != B200Q_DTYPE_F16 && dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  if (n_elems == 0 || (n_elems % 8) != 0) return B200Q_ERR_UNSUPPORTED_SHAPE;
+  if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) != 0)
+    return B200Q_ERR_MISALIGNED;
+  OneTripParams p{};
+  const size_t half = (recv_bytes / 2) & ~static_cast<size_t>(255);
+  if (static_cast<size_t>(world) * n_elems * 4 > half) return B200Q_ERR_WORKSPACE;
+  for (int r = 0; r < world; ++r) {
+    if (peer_recv[r] == nullptr || peer_flags[r] == nullptr) return B200Q_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(peer_recv[r]) & 255u) != 0) return B200Q_ERR_MISALIGNED;
+    p.recv[r] = peer_recv[r];
+  }
+  if (device_cc_major() != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+  p.ctl = static_cast<unsigned int*>(peer_flags[rank]);
+  p.half_bytes = half;
+  p.x = static_cast<const uint4*>(x);
+  p.y = static_cast<uint4*>(y);
+  p.n_chunks = n_elems / 8;
+  p.rank = rank;
+  p.world = world;
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return B200Q_ERR_LAUNCH;
+  // one chunk per thread until every SM has a CTA; never more CTAs than are resident at once
+  long long blocks = static_cast<long long>((p.n_chunks + kThreads - 1) / kThreads);
+  if (blocks > sm_count()) blocks = sm_count();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B200Q_DTYPE_BF16) {
+    tp_allreduce_onetrip_kernel<true><<<static_cast<int>(blocks), kThreads, 0, st>>>(p);
+  } else {
+    tp_allreduce_onetrip_kernel<false><<<static_cast<int>(blocks), kThreads, 0, st>>>(p);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     note_cuda_error(e);

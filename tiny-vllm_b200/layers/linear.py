@@ -37,15 +37,17 @@ _SCALE_NAMES = ("scales", "w_scales")
 
 
 # Optional replacement for the NCCL all-reduce after row-parallel layers: an object with
-# ``buffer(shape, dtype)`` and ``all_reduce_(tensor)`` (layers.tp_comm.PeerAllReduce).
+# ``reduce(tensor) -> tensor`` and, optionally, the fused decode hooks ``fused_fits`` /
+# ``fused_w8a8`` / ``fused_w8a16`` (layers.tp_comm.PeerAllReduce).
 _peer_all_reduce = None
 
 
 def set_tp_all_reduce(comm) -> None:
     """Routes the sum after every RowParallelLinear through ``comm`` (peer-memory kernel)
-    instead of ``dist.all_reduce``; ``None`` restores NCCL.  With a communicator the layer's
+    instead of ``dist.all_reduce``; ``None`` restores NCCL.  With a communicator a large
     result lives in one of its rotating symmetric slots: it stays valid until that many
-    further row-parallel calls have been made."""
+    further large row-parallel calls have been made.  Decode-sized quantized calls run the
+    GEMM and the sum as one kernel, small tensors take the one-trip all-reduce."""
     global _peer_all_reduce
     _peer_all_reduce = comm
 
@@ -277,10 +279,7 @@ class RowParallelLinear(LinearBase):
             # ``None`` bias lets the quant method pick ``self.bias`` on every rank.
             y = self.quant_method.apply(x, self, bias)
         if self.tp_size > 1:
-            if comm is not None and y.is_cuda and y.numel() % 8 == 0 \
-                    and y.numel() * y.element_size() <= comm.slot_bytes:
-                shared = comm.buffer(y.shape, y.dtype)
-                shared.copy_(y)
-                return comm.all_reduce_(shared)
+            if comm is not None and y.is_cuda:
+                return comm.reduce(y)
             dist.all_reduce(y)
         return y

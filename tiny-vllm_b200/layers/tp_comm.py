@@ -23,6 +23,7 @@ and the caller then uses the two-kernel route.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -60,6 +61,10 @@ class PeerAllReduce:
         self._pad_hdl = symm_mem.rendezvous(self._pad, name)
         # receive area and flags of the fused decode kernels
         self.fused_bytes = (fused_bytes + 511) // 512 * 512
+        # largest tensor the one-trip all-reduce takes: every rank sends (world - 1) copies at
+        # twice the size, so the cross-over with the two-shot kernel falls as the group grows
+        self.small_max_bytes = int(os.environ.get("B200Q_SMALL_ALLREDUCE_BYTES",
+                                                  (2 << 20) // self.world))
         self._recv = symm_mem.empty(self.fused_bytes, dtype=torch.uint8, device=dev)
         self._recv.zero_()
         self._recv_hdl = symm_mem.rendezvous(self._recv, name)
@@ -106,6 +111,39 @@ class PeerAllReduce:
                                            torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "b200q_tp_allreduce", f"n={t.numel()} world={self.world}")
         return t
+
+    def small_fits(self, t: torch.Tensor) -> bool:
+        """True when ``t`` qualifies for the one-trip kernel: 16-bit, contiguous, a multiple of
+        8 elements, at most ``small_max_bytes`` and within the receive area."""
+        return (t.is_cuda and t.dtype in _DTYPE_IDS and t.is_contiguous() and t.numel() > 0
+                and t.numel() % 8 == 0 and t.data_ptr() % 16 == 0
+                and t.numel() * 2 <= self.small_max_bytes
+                and self.world * t.numel() * 4 <= self.fused_bytes // 2)
+
+    def all_reduce_small_(self, t: torch.Tensor) -> torch.Tensor:
+        """Sums any local 16-bit tensor over the group in place with the one-trip kernel."""
+        rc = _lib.lib().b200q_tp_allreduce_small(
+            t.data_ptr(), t.data_ptr(), t.numel(), _DTYPE_IDS[t.dtype], self._recv_arr,
+            self._fflags_arr, self.fused_bytes, self.rank, self.world,
+            torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "b200q_tp_allreduce_small", f"n={t.numel()} world={self.world}")
+        return t
+
+    def reduce(self, y: torch.Tensor) -> torch.Tensor:
+        """Sum of ``y`` over the group by the cheapest route that takes it: the one-trip
+        kernel for small tensors, the two-shot kernel through a symmetric slot for large ones,
+        NCCL for everything else.  Returns the reduced tensor (``y`` itself or a slot)."""
+        if self.small_fits(y):
+            return self.all_reduce_small_(y)
+        if y.is_cuda and y.dtype in _DTYPE_IDS and y.numel() % 8 == 0 \
+                and y.numel() * y.element_size() <= self.slot_bytes:
+            if self.owns(y):
+                return self.all_reduce_(y)
+            shared = self.buffer(y.shape, y.dtype)
+            shared.copy_(y)
+            return self.all_reduce_(shared)
+        dist.all_reduce(y, group=self.group)
+        return y
 
     # ------------------------------------------------------------------ fused decode route
     def fused_fits(self, tokens: int, n_out: int) -> bool:
