@@ -63,8 +63,9 @@ class PeerAllReduce:
         self.fused_bytes = (fused_bytes + 511) // 512 * 512
         # largest tensor the one-trip all-reduce takes: every rank sends (world - 1) copies at
         # twice the size, so the cross-over with the two-shot kernel falls as the group grows
-        self.small_max_bytes = int(os.environ.get("B200Q_SMALL_ALLREDUCE_BYTES",
-                                                  (2 << 20) // self.world))
+        # (measured: 2 ranks about 2 MiB, 4 ranks about 400 KiB)
+        default_small = (1 << 20) if self.world <= 2 else (256 << 10) if self.world <= 4 else (128 << 10)
+        self.small_max_bytes = int(os.environ.get("B200Q_SMALL_ALLREDUCE_BYTES", default_small))
         self._recv = symm_mem.empty(self.fused_bytes, dtype=torch.uint8, device=dev)
         self._recv.zero_()
         self._recv_hdl = symm_mem.rendezvous(self._recv, name)
