@@ -135,6 +135,37 @@ def run_reference_arm(args):
 
 
 # --------------------------------------------------------------------------- GPU arm
+class GraphEventTimer:
+    """CUDA events that can be recorded inside a captured graph and read from outside
+    (cudaEventRecordWithFlags + cudaEventRecordExternal): torch's own events become plain
+    dependency edges when recorded during capture and carry no time stamp."""
+
+    def __init__(self):
+        import ctypes
+        self._c = ctypes
+        self._rt = ctypes.CDLL("libcudart.so.12")
+        self._rt.cudaEventCreate.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
+        self._rt.cudaEventRecordWithFlags.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint]
+        self._rt.cudaEventElapsedTime.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.c_void_p,
+                                                  ctypes.c_void_p]
+
+    def record(self, stream: int):
+        ev = self._c.c_void_p()
+        rc = self._rt.cudaEventCreate(self._c.byref(ev))
+        if rc == 0:
+            rc = self._rt.cudaEventRecordWithFlags(ev, self._c.c_void_p(stream), 1)  # external
+        if rc != 0:
+            raise RuntimeError(f"cudaEventRecordWithFlags failed with CUDA error {rc}")
+        return ev
+
+    def elapsed_ms(self, start, stop) -> float:
+        out = self._c.c_float()
+        rc = self._rt.cudaEventElapsedTime(self._c.byref(out), start, stop)
+        if rc != 0:
+            raise RuntimeError(f"cudaEventElapsedTime failed with CUDA error {rc}")
+        return float(out.value)
+
+
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -251,7 +282,11 @@ def run_gpu_arm(args):
     ws_bytes = max([L.b200q_workspace_bytes(_lib.OP_W8A8, TOKENS, w["N"], w["K"]) for w in work] + [16])
     ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
 
-    def kernel_step(events=None):
+    def kernel_step(events=None, marks=None):
+        """One pass of the hot path.  ``events``: eager mode, torch events around every GEMM.
+        ``marks``: capture mode, a list that receives (name, start, stop) externally visible
+        event handles recorded into the graph around every GEMM."""
+        stream = torch.cuda.current_stream().cuda_stream     # the capture stream while capturing
         for w in work:
             rc = L.b200q_act_quant_i8(w["x"].data_ptr(), w["K"], _lib.DTYPE_BF16, w["xq"].data_ptr(),
                                       w["a_s"].data_ptr(), TOKENS, w["K"], stream)
@@ -259,6 +294,8 @@ def run_gpu_arm(args):
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e0.record()
+            if marks is not None:
+                m0 = rt.record(stream)
             rc = L.b200q_w8a8_gemm(w["xq"].data_ptr(), w["a_s"].data_ptr(), w["layer"].qweight.data_ptr(),
                                    w["layer"].w_scales.data_ptr(), None, w["y"].data_ptr(), TOKENS,
                                    w["N"], w["K"], _lib.DTYPE_BF16, ws.data_ptr(), ws.numel(), stream)
@@ -267,6 +304,8 @@ def run_gpu_arm(args):
                 e1 = torch.cuda.Event(enable_timing=True)
                 e1.record()
                 events.append((w["name"], e0, e1))
+            if marks is not None:
+                marks.append((w["name"], m0, rt.record(stream)))
             if w["split"] == "row" and tp > 1:
                 if comm is not None:
                     comm.all_reduce_(w["y"])
@@ -309,6 +348,25 @@ def run_gpu_arm(args):
     if L.b200q_device_status() != 0:
         raise SystemExit("device status word set during warm-up: a bounded wait gave up")
 
+    # ---- capture: one CUDA graph per step, so that the timed region holds no host launch
+    # overhead.  A few copies of the graph, each with its own event pairs around the GEMMs,
+    # are replayed in turn: after the run they hold the GEMM durations of the last steps.
+    graphs, marks_of, per_graph = [], [], 0
+    if not args.no_graph:
+        rt = GraphEventTimer()
+        for _ in range(min(8, args.steps)):
+            marks = []
+            g = torch.cuda.CUDAGraph()
+            before = L.b200q_launch_count()
+            with torch.cuda.graph(g):
+                kernel_step(marks=marks)
+            per_graph = L.b200q_launch_count() - before
+            graphs.append(g)
+            marks_of.append(marks)
+        for g in graphs:
+            g.replay()
+        sync_all()
+
     # ---- timed region (device time, inputs resident in HBM)
     sampler = ClockSampler(local_rank) if rank == 0 else None
     launches0 = L.b200q_launch_count()
@@ -316,12 +374,16 @@ def run_gpu_arm(args):
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
     t_start.record()
-    for _ in range(args.steps):
-        kernel_step(events)
+    if graphs:
+        for i in range(args.steps):
+            graphs[i % len(graphs)].replay()
+    else:
+        for _ in range(args.steps):
+            kernel_step(events)
     t_end.record()
     sync_all()
     elapsed_ms = t_start.elapsed_time(t_end)
-    launches = L.b200q_launch_count() - launches0
+    launches = per_graph * args.steps if graphs else L.b200q_launch_count() - launches0
     clocks = sampler.stop() if sampler is not None else None
     if tp > 1:
         t = torch.tensor([elapsed_ms], device=dev)
@@ -336,6 +398,9 @@ def run_gpu_arm(args):
     gemm_ms_total, gemm_ops_total = 0.0, 0.0
     for name, e0, e1 in events:
         per_shape.setdefault(name, []).append(e0.elapsed_time(e1))
+    for marks in marks_of:
+        for name, m0, m1 in marks:
+            per_shape.setdefault(name, []).append(rt.elapsed_ms(m0, m1))
     ops_of = {w["name"]: w["ops"] for w in work}
     bytes_of = {w["name"]: TOKENS * w["K"] + w["N"] * w["K"] + 4 * TOKENS + 4 * w["N"] + 2 * TOKENS * w["N"]
                 for w in work}
@@ -390,6 +455,9 @@ def run_gpu_arm(args):
                        "tokens": TOKENS, "parallelism": f"tp{world}",
                        "allreduce": ("none" if world == 1 else
                                      "b200q_tp_allreduce (peer memory)" if comm is not None else "nccl"),
+                       "launch": ("one CUDA graph per step (act-quant + GEMM x 4); GEMM durations from "
+                                  "event nodes inside the graphs of the last timed steps" if graphs
+                                  else "eager launches through the C ABI"),
                        "l2": "no flush: one step touches about 450 MB (activations, int8 copies, outputs), "
                              "more than the 126 MB L2"},
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
@@ -493,6 +561,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every kernel from the host inside the timed region instead of "
+                         "replaying one CUDA graph per step")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="sum row-parallel outputs with NCCL instead of the peer-memory kernel")
     ap.add_argument("--mode", default="headline", choices=["headline", "shape_sweep"],

@@ -18,6 +18,7 @@
 #include <cuda_runtime.h>
 
 #include "common.h"
+#include "ptx_sm100.cuh"
 
 namespace b200q {
 namespace {
@@ -34,9 +35,34 @@ __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
   return __half22float2(*reinterpret_cast<__half2*>(&u));
 }
 
-__device__ __forceinline__ float absmax4(float m, const float2 a, const float2 b) {
-  return fmaxf(fmaxf(m, fmaxf(fabsf(a.x), fabsf(a.y))), fmaxf(fabsf(b.x), fabsf(b.y)));
-}
+// Running absolute maximum of a row, kept in the 16-bit domain: two elements per instruction.
+// |x| of a 16-bit float compares like the float itself, so the packed maximum of the packed
+// absolute values is exact; it is widened to fp32 once per thread.  (NaN elements are skipped,
+// as fmaxf would.)
+template <typename T>
+struct AbsMax2;
+template <>
+struct AbsMax2<__nv_bfloat16> {
+  __nv_bfloat162 m;
+  __device__ __forceinline__ AbsMax2() : m(__floats2bfloat162_rn(0.f, 0.f)) {}
+  __device__ __forceinline__ void add(uint32_t u) {
+    m = __hmax2(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&u)));
+  }
+  __device__ __forceinline__ float value() const {
+    return fmaxf(__low2float(m), __high2float(m));
+  }
+};
+template <>
+struct AbsMax2<__half> {
+  __half2 m;
+  __device__ __forceinline__ AbsMax2() : m(__floats2half2_rn(0.f, 0.f)) {}
+  __device__ __forceinline__ void add(uint32_t u) {
+    m = __hmax2(m, __habs2(*reinterpret_cast<const __half2*>(&u)));
+  }
+  __device__ __forceinline__ float value() const {
+    return fmaxf(__low2float(m), __high2float(m));
+  }
+};
 
 // Exact path for one element: clamp(rint(v / scale), -127, 127) as a byte (IEEE division).
 __device__ __forceinline__ uint32_t quant1_exact(float v, float scale) {
@@ -58,14 +84,16 @@ __device__ __noinline__ uint2 quant8_exact(const uint4 raw, float scale) {
 }
 
 // Eight elements -> eight int8 codes, bit-identical to the IEEE division.
-// Fast path: t = v * (1/scale) is within 2 ulp of the true quotient (|t| <= 127, so within
-// 1.6e-5), hence rint(t) can differ from rint(v / scale) only when t lies that close to a
-// rounding tie k + 0.5.  A chunk that has such an element (|t - rint(t)| > 0.4999, about
-// one chunk in 600 for random data) is redone with exact divisions.  Rounding uses the
-// 1.5 * 2^23 trick: adding the constant rounds half-to-even to an integer and leaves that
-// integer in the low mantissa bits (two's complement), i.e. the low byte is the int8 code.
-// |t| cannot exceed 127 (1 + 2^-22) because scale >= absmax / 127, so no clamp is needed.
-// Packed fp32x2 instructions round each half like the scalar ones.
+// Fast path: the exact product p = v * (1/scale) is within 1.3e-5 of the rounded quotient
+// fl(v / scale) (|p| <= 127; one rounding in the reciprocal, one in the quotient), hence
+// rint(p) can differ from rint(fl(v / scale)) only when p lies that close to a rounding tie
+// k + 0.5.  A chunk that has such an element (|p - rint(p)| > 0.4999, about one chunk in
+// 600 for random data) is redone with exact divisions.  Rounding uses the 1.5 * 2^23
+// trick: u = fma(v, 1/scale, 1.5 * 2^23) rounds p half-to-even to an integer and leaves
+// that integer in the low mantissa bits (two's complement), i.e. the low byte of u is the
+// int8 code; r = u - 1.5 * 2^23 is that integer exactly and fma(v, 1/scale, -r) the distance
+// to it.  |p| cannot exceed 127 (1 + 2^-22) because scale >= absmax / 127, so no clamp is
+// needed.  Packed fp32x2 instructions round each half like the scalar ones.
 template <typename T>
 __device__ __forceinline__ uint2 quant8(const uint4 raw, float scale, float inv_scale) {
   const float2 inv2 = make_float2(inv_scale, inv_scale);
@@ -76,10 +104,10 @@ __device__ __forceinline__ uint2 quant8(const uint4 raw, float scale, float inv_
   float worst = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 t = __fmul2_rn(unpack2<T>(w[i]), inv2);
-    const float2 u = __fadd2_rn(t, magic);
+    const float2 v = unpack2<T>(w[i]);
+    const float2 u = __ffma2_rn(v, inv2, magic);
     const float2 r = __fadd2_rn(u, neg_magic);
-    const float2 d = __fadd2_rn(t, make_float2(-r.x, -r.y));
+    const float2 d = __ffma2_rn(v, inv2, make_float2(-r.x, -r.y));
     worst = fmaxf(worst, fmaxf(fabsf(d.x), fabsf(d.y)));
     ub[2 * i] = __float_as_uint(u.x);
     ub[2 * i + 1] = __float_as_uint(u.y);
@@ -104,6 +132,8 @@ __global__ void __launch_bounds__(256)
 act_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ xq,
                       float* __restrict__ a_scales, int M, int K) {
   constexpr int kRowsPerBlock = 256 / G;
+  ptx::grid_dependency_wait();     // x may be the previous kernel's output
+  ptx::grid_launch_dependents();
   const int g = threadIdx.x / G;  // row group inside the block
   const int t = threadIdx.x % G;  // thread inside the group
   const int row = blockIdx.x * kRowsPerBlock + g;
@@ -112,7 +142,7 @@ act_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__
   const int nchunk = K >> 3;  // 8 elements per 16-byte chunk
 
   uint4 raw[CHUNKS];
-  float amax = 0.f;
+  AbsMax2<T> running;
   if (active) {
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx);
 #pragma unroll
@@ -122,11 +152,13 @@ act_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__
     }
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
-      amax = absmax4(amax, unpack2<T>(raw[c].x), unpack2<T>(raw[c].y));
-      amax = absmax4(amax, unpack2<T>(raw[c].z), unpack2<T>(raw[c].w));
+      running.add(raw[c].x);
+      running.add(raw[c].y);
+      running.add(raw[c].z);
+      running.add(raw[c].w);
     }
   }
-  amax = warp_max(amax);
+  float amax = warp_max(running.value());
   if (G > 32) {
     // the row's G/32 warps are neighbours in the block: combine their maxima
     constexpr int kWarpsPerRow = G / 32;
@@ -154,17 +186,21 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 act_quant_long_rows_kernel(const T* __restrict__ x, int64_t ldx, int8_t* __restrict__ xq,
                            float* __restrict__ a_scales, int M, int K) {
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
   const int row = blockIdx.x;
   __shared__ float red[8];
   const int nchunk = K >> 3;
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx);
-  float amax = 0.f;
+  AbsMax2<T> running;
   for (int idx = threadIdx.x; idx < nchunk; idx += 256) {
     const uint4 r = __ldg(src + idx);
-    amax = absmax4(amax, unpack2<T>(r.x), unpack2<T>(r.y));
-    amax = absmax4(amax, unpack2<T>(r.z), unpack2<T>(r.w));
+    running.add(r.x);
+    running.add(r.y);
+    running.add(r.z);
+    running.add(r.w);
   }
-  amax = warp_max(amax);
+  float amax = warp_max(running.value());
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
   __syncthreads();
   float m = red[0];
@@ -185,21 +221,20 @@ cudaError_t launch_typed(const T* x, int64_t ldx, int8_t* xq, float* a_scales, i
   // rows are spread over more threads instead of more chunks.
   auto blocks = [&](int g) { return (M + (256 / g) - 1) / (256 / g); };
   if (K <= 32 * 8 * 2) {
-    act_quant_rows_kernel<T, 32, 2><<<blocks(32), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+    return launch_overlapped(act_quant_rows_kernel<T, 32, 2>, blocks(32), 256, 0, s, x, ldx, xq, a_scales, M, K);
   } else if (K <= 32 * 8 * 4) {
-    act_quant_rows_kernel<T, 32, 4><<<blocks(32), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+    return launch_overlapped(act_quant_rows_kernel<T, 32, 4>, blocks(32), 256, 0, s, x, ldx, xq, a_scales, M, K);
   } else if (K <= 64 * 8 * 4) {
-    act_quant_rows_kernel<T, 64, 4><<<blocks(64), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+    return launch_overlapped(act_quant_rows_kernel<T, 64, 4>, blocks(64), 256, 0, s, x, ldx, xq, a_scales, M, K);
   } else if (K <= 128 * 8 * 4) {
-    act_quant_rows_kernel<T, 128, 4><<<blocks(128), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+    return launch_overlapped(act_quant_rows_kernel<T, 128, 4>, blocks(128), 256, 0, s, x, ldx, xq, a_scales, M, K);
   } else if (K <= 256 * 8 * 4) {
-    act_quant_rows_kernel<T, 256, 4><<<blocks(256), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+    return launch_overlapped(act_quant_rows_kernel<T, 256, 4>, blocks(256), 256, 0, s, x, ldx, xq, a_scales, M, K);
   } else if (K <= 256 * 8 * 8) {
-    act_quant_rows_kernel<T, 256, 8><<<blocks(256), 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+    return launch_overlapped(act_quant_rows_kernel<T, 256, 8>, blocks(256), 256, 0, s, x, ldx, xq, a_scales, M, K);
   } else {
-    act_quant_long_rows_kernel<T><<<M, 256, 0, s>>>(x, ldx, xq, a_scales, M, K);
+    return launch_overlapped(act_quant_long_rows_kernel<T>, M, 256, 0, s, x, ldx, xq, a_scales, M, K);
   }
-  return cudaGetLastError();
 }
 
 }  // namespace

@@ -121,6 +121,11 @@ int run_w8a8(GemmArgs& a) {
 
 }  // namespace
 
+bool pdl_enabled() {
+  static const bool on = env_int("B200Q_NO_PDL", 0) == 0;
+  return on;
+}
+
 int sm_count() {
   DeviceInfo* d = device_info();
   return d != nullptr && d->sms > 0 ? d->sms : 148;

@@ -90,6 +90,33 @@ int launch_w8a8_umma_pair(const GemmArgs& a);
 bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan);
 int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan);
 
+// Launches `kernel` so that it may overlap its start-up (barrier set-up, TMEM allocation,
+// descriptor prefetch, launch latency) with the tail of the previous kernel in the stream
+// (programmatic dependent launch).  Only for kernels that call ptx::grid_dependency_wait()
+// before their first access to global memory.  B200Q_NO_PDL=1 turns the overlap off.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+cudaError_t launch_maybe_overlapped(bool overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                    size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = (overlap && pdl_enabled()) ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  return launch_maybe_overlapped(true, kernel, grid, block, smem, stream,
+                                 static_cast<Args&&>(args)...);
+}
+
 void note_cuda_error(cudaError_t e);
 void count_launch(int n = 1);
 

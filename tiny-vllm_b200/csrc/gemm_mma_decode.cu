@@ -28,6 +28,7 @@
 
 #include "common.h"
 #include "peer_sync.cuh"
+#include "ptx_sm100.cuh"
 
 namespace b200q {
 namespace {
@@ -228,6 +229,8 @@ w8a8_mma_decode_kernel(const int8_t* __restrict__ xq, const int8_t* __restrict__
                        const FuseParams fp, int* status) {
   __shared__ int red[kWarps][MT * 16 * kChannels];
   __shared__ __align__(16) OutT part[FUSED ? MT * 16 * kChannels : 8];
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int ch = blockIdx.x * kChannels + g;
@@ -316,6 +319,8 @@ w8a16_mma_decode_kernel(const T* __restrict__ x, const int8_t* __restrict__ w,
                         T* __restrict__ y, int M, int N, int K, const FuseParams fp, int* status) {
   __shared__ float red[kWarps][MT * 16 * kChannels];
   __shared__ __align__(16) T part[FUSED ? MT * 16 * kChannels : 8];
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int ch = blockIdx.x * kChannels + g;
@@ -390,10 +395,18 @@ w8a16_mma_decode_kernel(const T* __restrict__ x, const int8_t* __restrict__ w,
   if (FUSED) exchange_and_sum<T>(part, fp, M, N, y, status);
 }
 
+// (Fused kernels are launched in plain stream order: a kernel that waits for other GPUs
+// does not start early.)
 // CTAs of a fused kernel wait for the same CTA of the peers, so every CTA of the grid has to
 // be resident at once: the launch is refused (the caller then takes the two-kernel route)
 // when the grid exceeds what the device holds.
 thread_local bool g_fused_refused = false;
+thread_local cudaError_t g_launch_error = cudaSuccess;
+cudaError_t take_launch_error() {
+  cudaError_t e = g_launch_error;
+  g_launch_error = cudaSuccess;
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
 template <typename Kernel>
 bool all_ctas_resident(Kernel kernel, int grid) {
   int per_sm = 0;
@@ -413,8 +426,9 @@ void launch_a8(const GemmArgs& a, int mt, const FuseParams& fp = FuseParams{}) {
     g_fused_refused = true;                                                                  \
     return;                                                                                  \
   }                                                                                          \
-  w8a8_mma_decode_kernel<OutT, MT, RAW, FUSED><<<grid, kThreads, 0, a.stream>>>(              \
-      xq, a.w, a.a_scales, a.w_scales, bias, out, a.M, a.N, a.K, fp, a.status)
+  g_launch_error = launch_maybe_overlapped(                                                  \
+      !FUSED, w8a8_mma_decode_kernel<OutT, MT, RAW, FUSED>, grid, kThreads, 0, a.stream, xq,  \
+      a.w, a.a_scales, a.w_scales, bias, out, a.M, a.N, a.K, fp, a.status)
   switch (mt) {
     case 1: B200Q_LAUNCH_A8(1); break;
     case 2: B200Q_LAUNCH_A8(2); break;
@@ -432,7 +446,8 @@ void launch_a16(const GemmArgs& a, int mt, const FuseParams& fp = FuseParams{}) 
     g_fused_refused = true;                                                                  \
     return;                                                                                  \
   }                                                                                          \
-  w8a16_mma_decode_kernel<T, MT, FUSED><<<grid, kThreads, 0, a.stream>>>(                     \
+  g_launch_error = launch_maybe_overlapped(                                                  \
+      !FUSED, w8a16_mma_decode_kernel<T, MT, FUSED>, grid, kThreads, 0, a.stream,             \
       reinterpret_cast<const T*>(a.x), a.w, a.w_scales, reinterpret_cast<const T*>(a.bias),   \
       reinterpret_cast<T*>(a.y), a.M, a.N, a.K, fp, a.status)
   switch (mt) {
@@ -458,7 +473,7 @@ cudaError_t launch_w8a8_mma_decode(const GemmArgs& a) {
   } else {
     launch_a8<__half, false>(a, mt);
   }
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = take_launch_error();
   if (e == cudaSuccess) count_launch();
   return e;
 }
@@ -471,7 +486,7 @@ cudaError_t launch_w8a16_mma_decode(const GemmArgs& a) {
   } else {
     launch_a16<__half>(a, mt);
   }
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = take_launch_error();
   if (e == cudaSuccess) count_launch();
   return e;
 }
@@ -504,7 +519,7 @@ static int finish_fused_launch() {
     g_fused_refused = false;
     return B200Q_ERR_UNSUPPORTED_SHAPE;
   }
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = take_launch_error();
   if (e != cudaSuccess) {
     note_cuda_error(e);
     return B200Q_ERR_LAUNCH;

@@ -84,6 +84,9 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above overlapped the previous kernel's tail; its results are needed from here
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
 
   const int total_items = p.tiles_a * p.tiles_b * p.splits;
 
@@ -411,8 +414,7 @@ cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const Ke
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  kern<<<plan.grid, kThreads, plan.smem_bytes, stream>>>(ta, tb, kp);
-  return cudaGetLastError();
+  return launch_overlapped(kern, plan.grid, kThreads, plan.smem_bytes, stream, ta, tb, kp);
 }
 
 }  // namespace

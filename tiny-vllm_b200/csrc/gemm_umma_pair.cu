@@ -111,6 +111,9 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   ptx::cluster_sync_all();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above overlapped the previous kernel's tail; its results are needed from here
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
 
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
@@ -285,8 +288,7 @@ cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const Pair
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  kern<<<grid, kThreads, kPairSmem, stream>>>(ta, tb, pp);
-  return cudaGetLastError();
+  return launch_overlapped(kern, grid, kThreads, kPairSmem, stream, ta, tb, pp);
 }
 
 }  // namespace

@@ -100,6 +100,9 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above overlapped the previous kernel's tail; its results are needed from here
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
 
   const int total_items = p.tiles_a * p.tiles_b * p.splits;
 
@@ -367,8 +370,7 @@ cudaError_t launch_kernel(const CUtensorMap& tx, const CUtensorMap& tw, const Ke
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  kern<<<plan.grid, kThreads, plan.smem_bytes, stream>>>(tx, tw, kp);
-  return cudaGetLastError();
+  return launch_overlapped(kern, plan.grid, kThreads, plan.smem_bytes, stream, tx, tw, kp);
 }
 
 }  // namespace

@@ -269,5 +269,18 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// ---- programmatic dependent launch.  A kernel launched with the programmatic-serialization
+// attribute may start while its predecessor in the stream is still running; it must not
+// touch memory the predecessor reads or writes before grid_dependency_wait(), which
+// returns once the predecessor grid has completed and its writes are visible.  Both are
+// no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets the next kernel in the stream begin launching (it still waits as described above).
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 }  // namespace ptx
 }  // namespace b200q
