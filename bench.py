@@ -352,7 +352,9 @@ def run_gpu_arm(args):
     # overhead.  A few copies of the graph, each with its own event pairs around the GEMMs,
     # are replayed in turn: after the run they hold the GEMM durations of the last steps.
     graphs, marks_of, per_graph = [], [], 0
-    if not args.no_graph:
+    # (NCCL collectives stay out of graph capture: with the NCCL route the step is launched
+    # from the host, kernel by kernel)
+    if not args.no_graph and (tp == 1 or comm is not None):
         rt = GraphEventTimer()
         for _ in range(min(8, args.steps)):
             marks = []
