@@ -282,10 +282,9 @@ def run_gpu_arm(args):
     ws_bytes = max([L.b200q_workspace_bytes(_lib.OP_W8A8, TOKENS, w["N"], w["K"]) for w in work] + [16])
     ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
 
-    def kernel_step(events=None, marks=None):
-        """One pass of the hot path.  ``events``: eager mode, torch events around every GEMM.
-        ``marks``: capture mode, a list that receives (name, start, stop) externally visible
-        event handles recorded into the graph around every GEMM."""
+    def kernel_step(events=None):
+        """One pass of the hot path.  ``events``: optional list that receives torch events
+        around every GEMM (eager launches only)."""
         stream = torch.cuda.current_stream().cuda_stream     # the capture stream while capturing
         for w in work:
             rc = L.b200q_act_quant_i8(w["x"].data_ptr(), w["K"], _lib.DTYPE_BF16, w["xq"].data_ptr(),
@@ -294,8 +293,6 @@ def run_gpu_arm(args):
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-            if marks is not None:
-                m0 = rt.record(stream)
             rc = L.b200q_w8a8_gemm(w["xq"].data_ptr(), w["a_s"].data_ptr(), w["layer"].qweight.data_ptr(),
                                    w["layer"].w_scales.data_ptr(), None, w["y"].data_ptr(), TOKENS,
                                    w["N"], w["K"], _lib.DTYPE_BF16, ws.data_ptr(), ws.numel(), stream)
@@ -304,8 +301,6 @@ def run_gpu_arm(args):
                 e1 = torch.cuda.Event(enable_timing=True)
                 e1.record()
                 events.append((w["name"], e0, e1))
-            if marks is not None:
-                marks.append((w["name"], m0, rt.record(stream)))
             if w["split"] == "row" and tp > 1:
                 if comm is not None:
                     comm.all_reduce_(w["y"])
@@ -349,24 +344,19 @@ def run_gpu_arm(args):
         raise SystemExit("device status word set during warm-up: a bounded wait gave up")
 
     # ---- capture: one CUDA graph per step, so that the timed region holds no host launch
-    # overhead.  A few copies of the graph, each with its own event pairs around the GEMMs,
-    # are replayed in turn: after the run they hold the GEMM durations of the last steps.
-    graphs, marks_of, per_graph = [], [], 0
+    # overhead and no event records (an event record between two kernels costs about 4 us of
+    # idle GPU per boundary here, 35 us per step)
+    step_graph, per_graph = None, 0
     # (NCCL collectives stay out of graph capture: with the NCCL route the step is launched
     # from the host, kernel by kernel)
     if not args.no_graph and (tp == 1 or comm is not None):
-        rt = GraphEventTimer()
-        for _ in range(min(8, args.steps)):
-            marks = []
-            g = torch.cuda.CUDAGraph()
-            before = L.b200q_launch_count()
-            with torch.cuda.graph(g):
-                kernel_step(marks=marks)
-            per_graph = L.b200q_launch_count() - before
-            graphs.append(g)
-            marks_of.append(marks)
-        for g in graphs:
-            g.replay()
+        step_graph = torch.cuda.CUDAGraph()
+        before = L.b200q_launch_count()
+        with torch.cuda.graph(step_graph):
+            kernel_step()
+        per_graph = L.b200q_launch_count() - before
+        for _ in range(3):
+            step_graph.replay()
         sync_all()
 
     # ---- timed region (device time, inputs resident in HBM)
@@ -376,16 +366,16 @@ def run_gpu_arm(args):
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
     t_start.record()
-    if graphs:
-        for i in range(args.steps):
-            graphs[i % len(graphs)].replay()
+    if step_graph is not None:
+        for _ in range(args.steps):
+            step_graph.replay()
     else:
         for _ in range(args.steps):
-            kernel_step(events)
+            kernel_step()
     t_end.record()
     sync_all()
     elapsed_ms = t_start.elapsed_time(t_end)
-    launches = per_graph * args.steps if graphs else L.b200q_launch_count() - launches0
+    launches = per_graph * args.steps if step_graph is not None else L.b200q_launch_count() - launches0
     clocks = sampler.stop() if sampler is not None else None
     if tp > 1:
         t = torch.tensor([elapsed_ms], device=dev)
@@ -395,14 +385,54 @@ def run_gpu_arm(args):
     full_ops = total_ops()
     value = full_ops / (ms_per_step * 1e-3) / 1e12
 
-    # per-kernel durations of the GEMM launches inside the timed region
-    per_shape = {}
+    # ---- per-kernel durations, right after the timed region: every kernel of the step is
+    # replayed as a graph of REPS back-to-back launches bracketed by two event nodes, so that
+    # the cost of the event records is spread over REPS launches
+    REPS, ROUNDS = 8, 6
+    rt = GraphEventTimer()
+
+    def batch_us(launch_one):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            cs = torch.cuda.current_stream().cuda_stream
+            m0 = rt.record(cs)
+            for _ in range(REPS):
+                launch_one(cs)
+            m1 = rt.record(cs)
+        g.replay()
+        torch.cuda.synchronize()
+        samples = []
+        for _ in range(ROUNDS):
+            g.replay()
+            torch.cuda.synchronize()
+            samples.append(rt.elapsed_ms(m0, m1) * 1e3 / REPS)
+        return sum(samples) / len(samples)
+
+    per_shape, aq_us = {}, {}
+    for w in work:
+        def one_gemm(cs, w=w):
+            _lib.check(L.b200q_w8a8_gemm(
+                w["xq"].data_ptr(), w["a_s"].data_ptr(), w["layer"].qweight.data_ptr(),
+                w["layer"].w_scales.data_ptr(), None, w["y"].data_ptr(), TOKENS, w["N"], w["K"],
+                _lib.DTYPE_BF16, ws.data_ptr(), ws.numel(), cs), "b200q_w8a8_gemm")
+
+        # the quantiser reads its input from HBM inside a step (nothing of x survives a step's
+        # 450 MB in L2), so its launches here rotate over REPS distinct copies of x
+        x_copies = [w["x"]] + [w["x"].clone() for _ in range(REPS - 1)]
+        turn = [0]
+
+        def one_quant(cs, w=w, x_copies=x_copies, turn=turn):
+            x = x_copies[turn[0] % REPS]
+            turn[0] += 1
+            _lib.check(L.b200q_act_quant_i8(x.data_ptr(), w["K"], _lib.DTYPE_BF16,
+                                            w["xq"].data_ptr(), w["a_s"].data_ptr(), TOKENS, w["K"], cs),
+                       "b200q_act_quant_i8")
+
+        per_shape[w["name"]] = [batch_us(one_gemm) * 1e-3]
+        aq_us[w["name"]] = batch_us(one_quant)
+        del x_copies
+    sync_all()
     gemm_ms_total, gemm_ops_total = 0.0, 0.0
-    for name, e0, e1 in events:
-        per_shape.setdefault(name, []).append(e0.elapsed_time(e1))
-    for marks in marks_of:
-        for name, m0, m1 in marks:
-            per_shape.setdefault(name, []).append(rt.elapsed_ms(m0, m1))
     ops_of = {w["name"]: w["ops"] for w in work}
     bytes_of = {w["name"]: TOKENS * w["K"] + w["N"] * w["K"] + 4 * TOKENS + 4 * w["N"] + 2 * TOKENS * w["N"]
                 for w in work}
@@ -423,6 +453,10 @@ def run_gpu_arm(args):
                 "frac": achieved / int8_peak, "traffic": traffic,
                 "traffic_note": "dram__bytes_read+write per launch, mean over the 4 shapes; algorithmic "
                                 "mean is 66.6 MB, the difference is output still dirty in L2 at kernel end",
+                "timing": f"CUDA event nodes around graphs of {REPS} back-to-back launches of each GEMM, "
+                          f"{ROUNDS} replays, taken right after the timed region (event records between "
+                          "the kernels of a step would add about 4 us of idle GPU per boundary); "
+                          "achieved = ops of the four GEMMs / sum of their durations",
                 "kernel": "w8a8_umma_pair_kernel (tcgen05 cta_group::2 kind::i8)" if world == 1 else "w8a8_umma kernels (tcgen05 kind::i8)",
                 "peak_note": f"2 x {peaks['source']} sustained bf16 dense TFLOP/s ({peaks['bf16_sustained']}); "
                              "int8 is the double-rate kind; nominal 4500"}
@@ -457,13 +491,16 @@ def run_gpu_arm(args):
                        "tokens": TOKENS, "parallelism": f"tp{world}",
                        "allreduce": ("none" if world == 1 else
                                      "b200q_tp_allreduce (peer memory)" if comm is not None else "nccl"),
-                       "launch": ("one CUDA graph per step (act-quant + GEMM x 4); GEMM durations from "
-                                  "event nodes inside the graphs of the last timed steps" if graphs
+                       "launch": ("one CUDA graph replay per step (act-quant + GEMM x 4, plus the "
+                                  "all-reduces at tp > 1)" if step_graph is not None
                                   else "eager launches through the C ABI"),
                        "l2": "no flush: one step touches about 450 MB (activations, int8 copies, outputs), "
                              "more than the 126 MB L2"},
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "device_status": status, "detail": detail,
+            "step_breakdown_us": {"step": ms_per_step * 1e3,
+                                  "gemm_sum": sum(v["gemm_us"] for v in detail.values()),
+                                  "act_quant_sum": sum(aq_us.values()), "act_quant": aq_us},
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline()
