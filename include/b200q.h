@@ -217,6 +217,34 @@ int b200q_w8a16_gemm_allreduce(const void* x, const int8_t* qweight, const float
                                size_t recv_bytes, int rank, int world, void* stream);
 
 /*
+ * Row-parallel W8A8 linear at prefill size with the all-reduce fused in: replaces the pair
+ * "quantized linear, then dist.all_reduce(y)" of RowParallelLinear.forward
+ * (nanovllm/layers/linear.py:265-276) by two kernels.
+ * Rank o owns token rows [o * M / world, (o + 1) * M / world).  Kernel 1 is the CTA-pair
+ * tcgen05 GEMM, whose epilogue writes every partial 128 x 256 tile (rounded to the output
+ * type, as b200q_w8a8_gemm would store it) straight into the owner's staging area, over
+ * NVLink when the owner is a peer: the reduce-scatter half of the all-reduce runs under the
+ * GEMM's main loop.  Kernel 2 exchanges one "GEMM complete" flag per peer (bounded wait),
+ * adds the `world` partials of the owned rows in rank order in fp32 from local memory and
+ * writes the result rows into every rank's output (all-gather half), then waits until
+ * every rank has done so.  Results are bit-identical on all ranks and to b200q_w8a8_gemm
+ * followed by b200q_tp_allreduce.
+ *
+ * HOST arrays of `world` DEVICE addresses as mapped into the calling process: peer_y (the
+ * output matrix [M, N], same symmetric allocation on every rank), peer_stage (staging area,
+ * stage_bytes >= M * N * 2), peer_flags (the control words of the fused kernels above,
+ * B200Q_FUSED_FLAG_BYTES; shared call numbering).  Every rank makes the same sequence of
+ * calls, ordered on one stream.  Limits: M % (world * 256) == 0, N % 8 == 0;
+ * B200Q_ERR_UNSUPPORTED_SHAPE otherwise (nothing launched).  A wait that runs out sets
+ * device status 0x701 / 0x702.
+ */
+int b200q_w8a8_gemm_allreduce_tiled(const int8_t* xq, const float* a_scales, const int8_t* qweight,
+                                    const float* w_scales, const void* bias, void* const* peer_y,
+                                    int M, int N, int K, int out_dtype, void* const* peer_stage,
+                                    size_t stage_bytes, void* const* peer_flags, int rank,
+                                    int world, void* stream);
+
+/*
  * Sum all-reduce of a SMALL 16-bit tensor over the tensor-parallel ranks in one NVLink trip
  * (same use as b200q_tp_allreduce, nanovllm/layers/linear.py:274-275, for tensors up to a
  * few hundred kilobytes, where two flag barriers cost more than the data).  x and y are

@@ -291,6 +291,127 @@ def _fused_worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
+def _tiled_worker(rank, world, port, out_dir):
+    """Prefill-sized row-parallel W8A8 layers: GEMM with the reduce-scatter in its epilogue +
+    sum-and-gather kernel, against GEMM + two-shot all-reduce and the CPU oracle."""
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import tiny_vllm_b200  # noqa: F401
+    from oracle import quant_linear_oracle as O
+    from tiny_vllm_b200 import _lib
+    from tiny_vllm_b200.layers import linear as LL
+    from tiny_vllm_b200.layers.tp_comm import PeerAllReduce
+    from tiny_vllm_b200.quantization.cuda import apply_w8a8_linear
+    ok, notes = True, []
+    try:
+        comm = PeerAllReduce(max_bytes=16 << 20, slots=2, tiled_prefill=True)
+        LL.set_tp_all_reduce(comm)
+        for dtype, M, N, K_local, with_bias in ((torch.bfloat16, 1024, 1024, 512, False),
+                                                (torch.float16, 2048, 384, 256, True),
+                                                (torch.bfloat16, 4096, 1000, 1024, False),
+                                                (torch.bfloat16, 1024, 1024, 512, False)):
+            K = K_local * world
+            q, s = O.make_weight(N, K, seed=41)
+            prev = torch.get_default_dtype()
+            torch.set_default_dtype(dtype)
+            with torch.device("cuda"):
+                layer = LL.RowParallelLinear(K, N, bias=with_bias, quantization="w8a8")
+            torch.set_default_dtype(prev)
+            layer.qweight.weight_loader(layer.qweight, q)
+            layer.w_scales.weight_loader(layer.w_scales, s)
+            if with_bias:
+                g = torch.Generator(device="cpu").manual_seed(5)
+                layer.bias.data.copy_(torch.randn(N, generator=g).to(dtype))
+            x = O.make_activation(M, K, seed=60 + N).to(dtype)
+            x_local = x.chunk(world, dim=1)[rank].contiguous().cuda()
+            assert comm.tiled_fits(M, N)
+            for rep in range(2):
+                y_fused = layer(x_local).clone()
+                x_q, a_s = layer.quant_method.quantize_activation(x_local)
+                part = apply_w8a8_linear(x_q, a_s, layer.qweight, layer.w_scales,
+                                         layer.bias, out_dtype=dtype)
+                buf = comm.buffer(part.shape, part.dtype)
+                buf.copy_(part)
+                y_two = comm.all_reduce_(buf).clone()
+                torch.cuda.synchronize()
+                if not torch.equal(y_fused.view(torch.int16), y_two.view(torch.int16)):
+                    ok = False
+                    bad = (y_fused.view(torch.int16) != y_two.view(torch.int16))
+                    rows = bad.any(dim=1).nonzero().flatten()
+                    notes.append(f"{dtype} M={M} N={N} rep {rep}: fused != two-kernel route, "
+                                 f"{int(bad.sum())} values in rows {rows[:4].tolist()}..{rows[-1:].tolist()}")
+            gathered = [torch.empty_like(y_fused) for _ in range(world)]
+            dist.all_gather(gathered, y_fused.contiguous())
+            if not all(torch.equal(g.view(torch.int16), y_fused.view(torch.int16)) for g in gathered):
+                ok = False
+                notes.append(f"M={M} N={N}: ranks disagree")
+            if M <= 2048:
+                bias_cpu = layer.bias.data.cpu() if with_bias else None
+                ref = torch.zeros(M, N)
+                for r in range(world):
+                    xq_r, as_r = O.quantize_per_row_dynamic(x.chunk(world, dim=1)[r].contiguous())
+                    acc = O.w8a8_int32_accumulators(xq_r, q.chunk(world, dim=1)[r].contiguous())
+                    ref += O.w8a8_native_epilogue(acc, as_r, s, bias_cpu, dtype).float()
+                if not torch.equal(ref.to(dtype).view(torch.int16), y_fused.cpu().view(torch.int16)):
+                    ok = False
+                    notes.append(f"{dtype} M={M} N={N}: differs from the oracle's rank-ordered sum")
+        ok = ok and _lib.lib().b200q_device_status() == 0
+        # timing at the bench shape: o_proj of Qwen3-0.6B, 8192 tokens
+        M, N, K = 8192, 1024, 2048
+        q, s = O.make_weight(N, K, seed=42)
+        torch.set_default_dtype(torch.bfloat16)
+        with torch.device("cuda"):
+            layer = LL.RowParallelLinear(K, N, quantization="w8a8")
+        torch.set_default_dtype(prev)
+        layer.qweight.weight_loader(layer.qweight, q)
+        layer.w_scales.weight_loader(layer.w_scales, s)
+        x_local = O.make_activation(M, K, seed=2).chunk(world, dim=1)[rank].contiguous().cuda()
+        x_q, a_s = layer.quant_method.quantize_activation(x_local)
+        buf = comm.buffer((M, N), torch.bfloat16)
+        y_plain = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+
+        def fused():
+            return comm.fused_w8a8_tiled(x_q, a_s, layer.qweight, layer.w_scales, None, torch.bfloat16)
+
+        def gemm_only():
+            return apply_w8a8_linear(x_q, a_s, layer.qweight, layer.w_scales, None, torch.bfloat16)
+
+        def two_shot():
+            comm.all_reduce_(buf)
+
+        def nccl():
+            dist.all_reduce(y_plain)
+
+        for fn, name in ((fused, "fused GEMM + reduce-scatter + gather"), (gemm_only, "GEMM alone"),
+                         (two_shot, "two-shot all-reduce alone"), (nccl, "NCCL all-reduce alone")):
+            notes.append(f"o_proj M=8192 tp={world} {name}: {_graph_time_us(fn, reps=10):.1f} us")
+        ok = ok and _lib.lib().b200q_device_status() == 0
+        LL.set_tp_all_reduce(None)
+    except Exception:  # noqa: BLE001
+        import traceback
+        ok = False
+        notes.append(traceback.format_exc())
+    torch.save({"ok": ok, "notes": notes}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_row_parallel_prefill_matches_two_kernel_route(tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    mp.spawn(_tiled_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        res = torch.load(tmp_path / f"r{r}.pt")
+        print(r, res["notes"])
+        assert res["ok"], res["notes"]
+
+
 def test_fused_row_parallel_decode_matches_two_kernel_route(tmp_path):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:

@@ -71,6 +71,10 @@ SIGNATURES = {
                                               _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                               _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int,
                                               _c.c_int, _c.c_void_p]),
+    "b200q_w8a8_gemm_allreduce_tiled": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                                   _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
+                                                   _c.c_int, _c.c_int, _c.c_void_p, _c.c_size_t,
+                                                   _c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p]),
     "b200q_tp_allreduce_small": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int,
                                             _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int,
                                             _c.c_int, _c.c_void_p]),

@@ -78,7 +78,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
         objs = list(pool.map(compile_one, SOURCES))
     cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *[str(o) for o in objs],
-           "-gencode", "arch=compute_100a,code=sm_100a"]
+           "-gencode", "arch=compute_100a,code=sm_100a",
+           "-Xlinker", "--no-undefined"]      # a launcher missing from every .cu fails the build
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)

@@ -235,6 +235,54 @@ int b200q_w8a8_gemm_allreduce(const int8_t* xq, const float* a_scales, const int
   return launch_w8a8_mma_decode_fused(a, peer_recv, peer_flags, recv_bytes, rank, world);
 }
 
+int b200q_w8a8_gemm_allreduce_tiled(const int8_t* xq, const float* a_scales, const int8_t* qweight,
+                                    const float* w_scales, const void* bias, void* const* peer_y,
+                                    int M, int N, int K, int out_dtype, void* const* peer_stage,
+                                    size_t stage_bytes, void* const* peer_flags, int rank,
+                                    int world, void* stream) {
+  if (xq == nullptr || a_scales == nullptr || qweight == nullptr || w_scales == nullptr ||
+      peer_y == nullptr || peer_stage == nullptr || peer_flags == nullptr)
+    return B200Q_ERR_NULL_POINTER;
+  if (int rc = check_dims(M, N, K)) return rc;
+  if (out_dtype != B200Q_DTYPE_F16 && out_dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return B200Q_ERR_BAD_ARGUMENT;
+  if ((N % 8) != 0 || (M % (world * 256)) != 0) return B200Q_ERR_UNSUPPORTED_SHAPE;
+  if (!aligned16(xq) || !aligned16(qweight) ||
+      (reinterpret_cast<uintptr_t>(a_scales) & 3u) != 0 ||
+      (reinterpret_cast<uintptr_t>(w_scales) & 3u) != 0 ||
+      (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 1u) != 0))
+    return B200Q_ERR_MISALIGNED;
+  if (static_cast<size_t>(M) * N * 2 > stage_bytes) return B200Q_ERR_WORKSPACE;
+  for (int r = 0; r < world; ++r) {
+    if (peer_y[r] == nullptr || peer_stage[r] == nullptr || peer_flags[r] == nullptr)
+      return B200Q_ERR_NULL_POINTER;
+    if (!aligned16(peer_y[r]) || !aligned16(peer_stage[r])) return B200Q_ERR_MISALIGNED;
+  }
+  DeviceInfo* d = device_info();
+  if (d == nullptr) return B200Q_ERR_LAUNCH;
+  if (d->cc_major != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+  GemmArgs a{};
+  a.x = xq;
+  a.w = qweight;
+  a.a_scales = a_scales;
+  a.w_scales = w_scales;
+  a.bias = bias;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.dtype = out_dtype;
+  a.status = d->status_ptr;
+  a.stream = static_cast<cudaStream_t>(stream);
+  // test hook: 1 = GEMM kernel only, 2 = sum-and-gather kernel only (two calls make one)
+  const int only = env_int("B200Q_DEBUG_TILED", 0);
+  if (!(only & 2)) {
+    if (int rc = launch_w8a8_umma_pair_scatter(a, peer_stage, rank, world)) return rc;
+  }
+  if (only & 1) return B200Q_OK;
+  return launch_tp_reduce_gather(peer_stage[rank], peer_y, peer_flags, rank, world, M, N,
+                                 out_dtype, a.stream);
+}
+
 int b200q_w8a16_gemm_allreduce(const void* x, const int8_t* qweight, const float* scales,
                                const void* bias, void* y, int M, int N, int K, int x_dtype,
                                void* const* peer_recv, void* const* peer_flags,

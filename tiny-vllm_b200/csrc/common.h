@@ -85,6 +85,13 @@ int env_int(const char* name, int dflt);
 // gemm_umma_pair.cu: CTA-pair (cta_group::2) variant for prefill-sized W8A8 problems
 bool umma_pair_applicable(int M, int N, int K, bool raw_int32_out);
 int launch_w8a8_umma_pair(const GemmArgs& a);
+// Row-parallel prefill: the pair kernel writing its partial tiles to the owners' staging areas
+// (reduce-scatter under the main loop), and the kernel that sums and gathers them.
+int launch_w8a8_umma_pair_scatter(const GemmArgs& a, void* const* peer_stage, int rank,
+                                  int world);
+int launch_tp_reduce_gather(const void* stage, void* const* peer_y,
+                            void* const* peer_ctl, int rank, int world, int M, int N, int dtype,
+                            cudaStream_t stream);
 
 // gemm_umma_w8a16.cu
 bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan);

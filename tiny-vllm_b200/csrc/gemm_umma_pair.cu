@@ -53,10 +53,37 @@ struct PairParams {
   int debug_flags;  // test-only: 1 = skip epilogue work, 4 = skip the global stores
 };
 
-template <typename OutT>
+// Row-parallel layers at prefill size: instead of its own output matrix, the SCATTER kernel
+// writes every 128 x 256 partial tile into the staging area of the rank that owns those token
+// rows (rank o owns rows [o * M / world, (o + 1) * M / world)), slot `rank`, with the same
+// 16-byte stores — over NVLink when the owner is a peer.  The transfer of the reduce-scatter
+// half of the all-reduce thus runs under the GEMM's main loop.  Nothing is signalled from
+// inside the kernel: its completion (stream order) is what tp_reduce_gather_kernel
+// (tp_allreduce.cu) announces to the peers.  (Per-tile flags raised behind a system fence
+// were measured too: the fences stalled the epilogue, 40-50 us against 30 us per GEMM.)
+struct ScatterParams {
+  void* stage[8];            // every rank's staging area: [src rank][M / world][N] values
+  int rank, world;
+  int rows_per_owner;        // M / world, a multiple of 256
+};
+
+// Order in which a pair walks the 256-row tiles.  Plain kernel: top to bottom.  SCATTER: the
+// owners take turns (starting with a different one on every rank), so that the pushes over
+// NVLink are spread over the whole kernel and over all links instead of coming in one burst
+// per owner.
+template <bool SCATTER>
+__device__ __forceinline__ int row_tile_of(int i, int tiles_a2, const ScatterParams& sp) {
+  if (!SCATTER) return i;
+  const int per_owner = tiles_a2 / sp.world;
+  const int owner = (i + sp.rank) % sp.world;
+  return owner * per_owner + i / sp.world;
+}
+
+template <typename OutT, bool SCATTER>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                      const __grid_constant__ CUtensorMap tmap_b, const PairParams pp) {
+                      const __grid_constant__ CUtensorMap tmap_b, const PairParams pp,
+                      const ScatterParams sp) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* staging = smem + kPairStages * kPairStageBytes;
   float* s_ws = reinterpret_cast<float*>(staging + kStagingBytes);
@@ -128,7 +155,7 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int item = pair; ok && item < total_items; item += num_pairs) {
         const int tile_b = item % pp.tiles_b;  // column tiles fastest: neighbours write one row band
-        const int tile_a2 = item / pp.tiles_b;
+        const int tile_a2 = row_tile_of<SCATTER>(item / pp.tiles_b, pp.tiles_a2, sp);
         const int row_a = (tile_a2 * 2 + static_cast<int>(rank)) * kTileA;
         const int row_b = tile_b * kPairBN + static_cast<int>(rank) * kHalfBN;
         for (int kb = 0; kb < pp.k_blocks; ++kb) {
@@ -207,7 +234,7 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int it = 0;
     for (int item = pair; item < total_items; item += num_pairs, ++it) {
       const int tile_b = item % pp.tiles_b;
-      const int tile_a2 = item / pp.tiles_b;
+      const int tile_a2 = row_tile_of<SCATTER>(item / pp.tiles_b, pp.tiles_a2, sp);
       const int tile_a = tile_a2 * 2 + static_cast<int>(rank);
       const int buf = it & 1;
       const uint32_t tphase = static_cast<uint32_t>(it >> 1) & 1u;
@@ -218,6 +245,12 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       const int row = tile_a * kTileA + row_in_tile;
       const float a_s = row < pp.M ? __ldg(pp.a_scales + row) : 0.f;
+      if (SCATTER) {
+        // this tile's rows belong to one owner: redirect the output there
+        const int owner = (tile_a * kTileA) / sp.rows_per_owner;
+        p.out = reinterpret_cast<OutT*>(sp.stage[owner]) +
+                static_cast<ptrdiff_t>(sp.rank - owner) * sp.rows_per_owner * pp.N;
+      }
       ptx::named_bar_sync(2, kEpiThreads);
       if (!ptx::mbar_wait(ptx::smem_u32(tfull_bar + buf), tphase, abort_flag)) break;
       ptx::tc_fence_after_sync();
@@ -276,19 +309,19 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-template <typename OutT>
+template <typename OutT, bool SCATTER = false>
 cudaError_t launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const PairParams& pp,
-                        int grid, cudaStream_t stream) {
+                        int grid, cudaStream_t stream, const ScatterParams& sp = ScatterParams{}) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = w8a8_umma_pair_kernel<OutT>;
+  auto kern = w8a8_umma_pair_kernel<OutT, SCATTER>;
   if (dev < 64 && !attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  return launch_overlapped(kern, grid, kThreads, kPairSmem, stream, ta, tb, pp);
+  return launch_overlapped(kern, grid, kThreads, kPairSmem, stream, ta, tb, pp, sp);
 }
 
 }  // namespace
@@ -301,6 +334,43 @@ bool umma_pair_applicable(int M, int N, int K, bool raw_int32_out) {
   const long long pair_tiles =
       static_cast<long long>((M + 255) / 256) * ((N + kPairBN - 1) / kPairBN);
   return M >= 512 && pair_tiles >= sm_count() / 2;
+}
+
+// Scatter variant for row-parallel layers: partial tiles go to the owners' staging areas.
+int launch_w8a8_umma_pair_scatter(const GemmArgs& a, void* const* peer_stage, int rank,
+                                  int world) {
+  CUtensorMap ta, tb;
+  if (!get_tensor_map(a.x, a.M, a.K, kTileA, kBlockK, &ta)) return B200Q_ERR_LAUNCH;
+  if (!get_tensor_map(a.w, a.N, a.K, kHalfBN, kBlockK, &tb)) return B200Q_ERR_LAUNCH;
+  PairParams pp{};
+  pp.M = a.M;
+  pp.N = a.N;
+  pp.K = a.K;
+  pp.tiles_a2 = (a.M + 255) / 256;
+  pp.tiles_b = (a.N + kPairBN - 1) / kPairBN;
+  pp.k_blocks = (a.K + kBlockK - 1) / kBlockK;
+  pp.a_scales = a.a_scales;
+  pp.w_scales = a.w_scales;
+  pp.bias = a.bias;
+  pp.out = nullptr;
+  pp.status = a.status;
+  pp.debug_flags = 0;
+  ScatterParams sp{};
+  for (int r = 0; r < world; ++r) sp.stage[r] = peer_stage[r];
+  sp.rank = rank;
+  sp.world = world;
+  sp.rows_per_owner = a.M / world;
+  const long long items = static_cast<long long>(pp.tiles_a2) * pp.tiles_b;
+  const int pairs = static_cast<int>(std::min<long long>(items, sm_count() / 2));
+  cudaError_t e = a.dtype == B200Q_DTYPE_BF16
+                      ? launch_pair<__nv_bfloat16, true>(ta, tb, pp, pairs * 2, a.stream, sp)
+                      : launch_pair<__half, true>(ta, tb, pp, pairs * 2, a.stream, sp);
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  count_launch();
+  return B200Q_OK;
 }
 
 int launch_w8a8_umma_pair(const GemmArgs& a) {

@@ -201,7 +201,153 @@ tp_allreduce_onetrip_kernel(const OneTripParams p) {
   }
 }
 
+// ------------------------------------------------- second half of the fused prefill all-reduce
+// The scatter GEMMs (gemm_umma_pair.cu) have put every rank's partial tiles for the token
+// rows this rank owns into the local staging area.  This kernel first exchanges one flag per
+// peer ("my scatter GEMM has completed": true by stream order when this kernel starts),
+// then sums the `world` partials in rank order in fp32 — local loads only — and writes the
+// result rows into EVERY rank's output matrix with 16-byte peer stores (the all-gather
+// half).  It ends with the same "my writes are done" barrier as the two-shot kernel, using
+// the shared call numbering of the tagged-word kernels.
+constexpr int kCtlReady = 24;  // control words [kCtlReady + src]: src's scatter GEMM is complete
+constexpr int kCtlDone = 16;  // control words [kCtlDone + src]: src finished writing (call number)
+
+struct GatherParams {
+  const void* stage;           // local staging: [src][rows_per_owner][N] values
+  void* y[kMaxWorld];          // every rank's output matrix [M][N]
+  unsigned int* ctl[kMaxWorld];
+  int rank, world;
+  int rows_per_owner, N, tiles_b;
+  int* status;
+};
+
+// W = compile-time bound on the number of ranks, U = chunks per thread in flight (U * W loads
+// are issued before the first use).
+template <bool BF16, int W, int U>
+__global__ void __launch_bounds__(kThreads)
+tp_reduce_gather_kernel(const GatherParams p) {
+  __shared__ unsigned int s_epoch;
+  __shared__ int s_flag;  // 0 ok, 1 = a wait gave up, 2 / 3 = this CTA is the rank's last (ok / failed)
+  unsigned int* ctl = p.ctl[p.rank];
+  if (threadIdx.x == 0) {
+    s_epoch = next_epoch(ctl);
+    s_flag = 0;
+  }
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
+  const int row_blocks = p.rows_per_owner / 128;
+  const int n_tiles = row_blocks * p.tiles_b;
+  const size_t slot_chunks = static_cast<size_t>(p.rows_per_owner) * p.N / 8;
+  const int row_chunks = p.N / 8;  // 16-byte chunks per matrix row
+  const uint4* stage = static_cast<const uint4*>(p.stage);
+
+  // every rank's scatter GEMM has completed (stream order on the sender, one flag per peer)
+  if (threadIdx.x < p.world) {
+    if (blockIdx.x == 0) st_release_sys(p.ctl[threadIdx.x] + kCtlReady + p.rank, epoch);
+    if (!wait_flag(ctl + kCtlReady + threadIdx.x, epoch)) s_flag = 1;
+  }
+  __syncthreads();
+  const bool ready = s_flag == 0;
+  for (int t = blockIdx.x; ready && t < n_tiles; t += gridDim.x) {
+    const int block = t / p.tiles_b, tile_b = t - block * p.tiles_b;
+    // 128 rows x 32 chunks of 16 bytes, U chunks per thread per round
+    for (int c0 = threadIdx.x; c0 < 128 * 32; c0 += kThreads * U) {
+      uint4 v[U][W];
+      size_t off[U];
+      bool live[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int c = c0 + u * kThreads;
+        const int r = c >> 5, cc = (c & 31) + tile_b * 32;
+        live[u] = c < 128 * 32 && cc < row_chunks;
+        off[u] = static_cast<size_t>(block * 128 + r) * row_chunks + cc;
+#pragma unroll
+        for (int src = 0; src < W; ++src)
+          if (src < p.world && live[u]) v[u][src] = ld_volatile16(stage + src * slot_chunks + off[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (!live[u]) continue;
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+        for (int src = 0; src < W; ++src)
+          if (src < p.world) accumulate<BF16>(acc, v[u][src]);
+        const uint4 out = pack<BF16>(acc);
+        const size_t yoff = static_cast<size_t>(p.rank) * slot_chunks + off[u];
+#pragma unroll
+        for (int dst = 0; dst < W; ++dst)
+          if (dst < p.world) st_peer16(static_cast<uint4*>(p.y[dst]) + yoff, out);
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(ctl + kCtlCounter, 1u);
+    if (done == gridDim.x - 1) {
+      ctl[kCtlCounter] = 0u;
+      s_flag = s_flag == 0 ? 2 : 3;
+    }
+  }
+  __syncthreads();
+  if (s_flag >= 2) {
+    __threadfence_system();
+    if (threadIdx.x < p.world) {
+      st_release_sys(p.ctl[threadIdx.x] + kCtlDone + p.rank, epoch);
+      if (!wait_flag(ctl + kCtlDone + threadIdx.x, epoch)) atomicCAS(p.status, 0, 0x702);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (s_flag == 3) atomicCAS(p.status, 0, 0x701);
+      *reinterpret_cast<volatile unsigned int*>(ctl + kCtlEpoch) = epoch;
+    }
+  } else if (s_flag == 1 && threadIdx.x == 0) {
+    atomicCAS(p.status, 0, 0x701);
+  }
+}
+
 }  // namespace
+
+int launch_tp_reduce_gather(const void* stage, void* const* peer_y,
+                            void* const* peer_ctl, int rank, int world, int M, int N, int dtype,
+                            cudaStream_t stream) {
+  GatherParams p{};
+  p.stage = stage;
+  for (int r = 0; r < world; ++r) {
+    p.y[r] = peer_y[r];
+    p.ctl[r] = static_cast<unsigned int*>(peer_ctl[r]);
+  }
+  p.rank = rank;
+  p.world = world;
+  p.rows_per_owner = M / world;
+  p.N = N;
+  p.tiles_b = (N + 255) / 256;
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return B200Q_ERR_LAUNCH;
+  const int n_tiles = (p.rows_per_owner / 128) * p.tiles_b;
+  const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
+#define B200Q_RG_LAUNCH(BF, W, U) tp_reduce_gather_kernel<BF, W, U><<<grid, kThreads, 0, stream>>>(p)
+  if (dtype == B200Q_DTYPE_BF16) {
+    if (world <= 2) B200Q_RG_LAUNCH(true, 2, 8);
+    else if (world <= 4) B200Q_RG_LAUNCH(true, 4, 4);
+    else B200Q_RG_LAUNCH(true, 8, 2);
+  } else {
+    if (world <= 2) B200Q_RG_LAUNCH(false, 2, 8);
+    else if (world <= 4) B200Q_RG_LAUNCH(false, 4, 4);
+    else B200Q_RG_LAUNCH(false, 8, 2);
+  }
+#undef B200Q_RG_LAUNCH
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  count_launch();
+  return B200Q_OK;
+}
+
 }  // namespace b200q
 
 extern "C" int b200q_tp_allreduce(void* const* peer_buffers, void* const* peer_flag_pads, int rank,

@@ -36,13 +36,20 @@ class W8A8QuantMethod(QuantMethod):
         )
 
     def apply_row_parallel(self, x: torch.Tensor, layer: nn.Module, bias, comm):
-        """Quantise, multiply and sum over the tensor-parallel ranks in one GEMM kernel
-        (decode-sized batches); ``None`` when the fused kernel does not take the shape."""
+        """Quantise, multiply and sum over the tensor-parallel ranks with the exchange fused
+        into the GEMM: one kernel for decode-sized batches, GEMM + reduce-scatter under the
+        main loop followed by a sum-and-gather kernel for prefill-sized ones.  ``None`` when
+        neither takes the shape."""
         n_out = layer.qweight.shape[0]
         tokens = x.numel() // x.shape[-1]
-        if not comm.fused_fits(tokens, n_out):
+        small = comm.fused_fits(tokens, n_out)
+        large = not small and getattr(comm, "tiled_fits", lambda *_: False)(tokens, n_out)
+        if not (small or large) or x.dtype not in (torch.float16, torch.bfloat16):
             return None
         x_q, a_scales = self.quantize_activation(x)
         chosen = layer.bias if bias is None else bias
-        y = comm.fused_w8a8(x_q, a_scales, layer.qweight, layer.w_scales, chosen, x.dtype)
+        if chosen is not None:
+            chosen = chosen.contiguous()
+        fused = comm.fused_w8a8 if small else comm.fused_w8a8_tiled
+        y = fused(x_q, a_scales, layer.qweight, layer.w_scales, chosen, x.dtype)
         return None if y is None else y.view(*x.shape[:-1], n_out)
