@@ -210,10 +210,9 @@ def _fused_worker(rank, world, port, out_dir):
                 buf.copy_(part)
                 y_two = comm.all_reduce_(buf)
                 torch.cuda.synchronize()
-                if scheme == "w8a8" or M <= 32:
-                    same = torch.equal(y_fused.view(torch.int16), y_two.view(torch.int16))
-                else:   # W8A16 above 32 tokens: the unfused route sums K in another order
-                    same = O.tensor_metrics(y_two, y_fused)["relative_l2"] < 4e-3
+                # (the unfused route runs the same decode kernel for these shapes, so W8A16 sums
+                # K in the same order too)
+                same = torch.equal(y_fused.view(torch.int16), y_two.view(torch.int16))
                 expect_launches = 2 if scheme == "w8a8" else 1   # act-quant + GEMM / GEMM
                 if not same or n_fused != expect_launches:
                     ok = False

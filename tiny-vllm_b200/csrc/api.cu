@@ -62,20 +62,24 @@ int check_dims(int M, int N, int K) {
 }
 
 // Kernel family for a W8A8 problem when nothing is forced.
+// The weight-streaming mma.sync kernel re-reads the activations once per 8 output channels,
+// so its range shrinks as N grows; thresholds from graph-replayed launches of the
+// Qwen3-0.6B projections at M = 32, 48, 64 (e.g. M = 48: 4.6 vs 7.6 us for 2048 -> 1024,
+// 7.3 vs 6.4 us for 1024 -> 6144).
 int auto_path_w8a8(int M, int N, int K) {
-  (void)N;
   (void)K;
   if (M <= env_int("B200Q_DEBUG_SIMT_MAX_M", 0)) return B200Q_PATH_SIMT_STREAM;
-  if (M <= 32) return B200Q_PATH_MMA_STREAM;
+  if (M <= 32 || (M <= 48 && N <= 4096) || (M <= 64 && N <= 2048)) return B200Q_PATH_MMA_STREAM;
   return B200Q_PATH_UMMA;
 }
 
 // Kernel family for a W8A16 problem when nothing is forced.
+// Same for W8A16, where the tcgen05 kernel's expansion stage costs more at small M
+// (M = 64: 7.2 vs 17.7 us for 2048 -> 1024, 12.4 vs 11.0 us for 1024 -> 6144).
 int auto_path_w8a16(int M, int N, int K) {
-  (void)N;
   (void)K;
   if (M <= env_int("B200Q_DEBUG_SIMT_MAX_M", 0)) return B200Q_PATH_SIMT_STREAM;
-  if (M <= 32) return B200Q_PATH_MMA_STREAM;
+  if (M <= 48 || (M <= 64 && N <= 4096)) return B200Q_PATH_MMA_STREAM;
   return B200Q_PATH_UMMA;
 }
 
