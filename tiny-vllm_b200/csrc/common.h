@@ -39,6 +39,7 @@ struct UmmaPlan {
   int splits;        // split-K factor
   int kb_per_split;
   int stages;        // shared-memory ring depth
+  int conv_bufs;     // W8A16 only: ring depth of the converted (16-bit) weight tiles
   int tmem_cols;     // power of two >= 2 * bn
   int grid;          // CTAs launched (persistent)
   size_t smem_bytes;

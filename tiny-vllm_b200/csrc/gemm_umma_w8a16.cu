@@ -51,14 +51,14 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint32_t stage_bytes = tile16_bytes + raw_bytes;
   const uint32_t conv_bytes = rows8 * kRow16;
   uint8_t* conv_base = smem + static_cast<size_t>(p.stages) * stage_bytes;
-  uint8_t* staging = conv_base + kConvBufs * conv_bytes;
+  uint8_t* staging = conv_base + p.conv_bufs * conv_bytes;
   float* s_ws = reinterpret_cast<float*>(staging + kStagingBytes);
   uint8_t* ctrl = reinterpret_cast<uint8_t*>(s_ws) + kScaleSmemBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
-  uint64_t* cfull_bar = empty_bar + kMaxStages;     // [kConvBufs] converted tile ready
-  uint64_t* cempty_bar = cfull_bar + kConvBufs;     // [kConvBufs] converted tile consumed
-  uint64_t* tfull_bar = cempty_bar + kConvBufs;
+  uint64_t* cfull_bar = empty_bar + kMaxStages;     // [conv_bufs] converted tile ready
+  uint64_t* cempty_bar = cfull_bar + kMaxConvBufs;  // [conv_bufs] converted tile consumed
+  uint64_t* tfull_bar = cempty_bar + kMaxConvBufs;
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -77,7 +77,7 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
       ptx::mbar_init(ptx::smem_u32(full_bar + s), 1);
       ptx::mbar_init(ptx::smem_u32(empty_bar + s), 1);
     }
-    for (int c = 0; c < kConvBufs; ++c) {
+    for (int c = 0; c < p.conv_bufs; ++c) {
       ptx::mbar_init(ptx::smem_u32(cfull_bar + c), kConvWarps);
       ptx::mbar_init(ptx::smem_u32(cempty_bar + c), 1);
     }
@@ -185,7 +185,7 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
             stage = 0;
             phase ^= 1u;
           }
-          if (++cb == kConvBufs) {
+          if (++cb == p.conv_bufs) {
             cb = 0;
             cphase ^= 1u;
           }
@@ -211,8 +211,13 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         const uint8_t* raw = smem + stage * stage_bytes + tile16_bytes;
         uint8_t* dst = conv_base + cb * conv_bytes;
-        if (!(p.debug_flags & 8))
-          for (int r = ctid; r < rows8; r += kConvThreads) expand_row<T>(raw, dst, r);
+        if (!(p.debug_flags & 8)) {
+          if (rows8 * 4 <= kConvThreads) {
+            if (ctid < rows8 * 4) expand_quarter_row<T>(raw, dst, ctid >> 2, ctid & 3);
+          } else {
+            for (int r = ctid; r < rows8; r += kConvThreads) expand_row<T>(raw, dst, r);
+          }
+        }
         ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the UMMA reads
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(cfull_bar + cb));
@@ -220,7 +225,7 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
           stage = 0;
           phase ^= 1u;
         }
-        if (++cb == kConvBufs) {
+        if (++cb == p.conv_bufs) {
           cb = 0;
           cphase ^= 1u;
         }
@@ -422,7 +427,10 @@ bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan) {
   const int rows16 = swap ? bn : kTileA;
   const int rows8 = swap ? kTileA : bn;
   const int stage_bytes = rows16 * kRow16 + rows8 * kRow8;
-  const int fixed = kConvBufs * rows8 * kRow16 + kStagingBytes + kScaleSmemBytes + kCtrlBytes;
+  // deeper ring of converted tiles where they are small: the expand -> MMA -> release chain
+  // takes about a microsecond per K block, so two buffers cap a narrow tile at 0.5 us per block
+  pl.conv_bufs = rows8 <= 64 ? 8 : rows8 <= 128 ? 4 : 2;
+  const int fixed = pl.conv_bufs * rows8 * kRow16 + kStagingBytes + kScaleSmemBytes + kCtrlBytes;
   int stages = (kMaxSmem - fixed) / stage_bytes;
   stages = std::min(stages, kMaxStages);
   stages = std::min(stages, std::max(2, pl.kb_per_split));
@@ -463,6 +471,7 @@ int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan) {
   kp.splits = plan.splits;
   kp.kb_per_split = plan.kb_per_split;
   kp.stages = plan.stages;
+  kp.conv_bufs = plan.conv_bufs;
   kp.tmem_cols = plan.tmem_cols;
   kp.swap = plan.swap;
   kp.n_channels = a.N;

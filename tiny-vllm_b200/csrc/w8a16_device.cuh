@@ -21,13 +21,13 @@ constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kConvWarps = 8;      // two per scheduler: the expansion is latency-bound per warp
 constexpr int kConvThreads = kConvWarps * 32;
 constexpr int kThreads = 64 + kEpiThreads + kConvThreads;
-constexpr int kConvBufs = 2;
+constexpr int kMaxConvBufs = 8;    // ring of converted tiles: 2 for 256-row tiles, more for narrow ones
 constexpr int kMaxStages = 8;
 constexpr int kMaxSmem = 227 * 1024;
 constexpr int kSlabBytes = 32 * 128;  // per-epilogue-warp transpose buffer (32 rows x 64 cols x 2 B)
 constexpr int kStagingBytes = kEpiWarps * kSlabBytes;
 constexpr int kScaleSmemBytes = 2 * 256 * 4;
-constexpr int kCtrlBytes = 256;
+constexpr int kCtrlBytes = 512;
 
 struct KernelParams {
   int rows_a, rows_b;
@@ -35,6 +35,7 @@ struct KernelParams {
   int tiles_a, tiles_b;
   int k_blocks, splits, kb_per_split;
   int stages;
+  int conv_bufs;
   int tmem_cols;
   int swap;
   int n_channels;
@@ -130,6 +131,18 @@ __device__ __forceinline__ void expand_row(const uint8_t* raw, uint8_t* dst, int
     *reinterpret_cast<uint4*>(dst_row + (((2 * c + 1) ^ sw16) << 4)) =
         make_uint4(e2.x, e2.y, e3.x, e3.y);
   }
+}
+
+// A quarter of a row (16 int8 -> 32 bytes of the 16-bit tile): narrow tiles are spread over
+// all converter threads so that one K block costs one short dependent chain per thread.
+template <typename T>
+__device__ __forceinline__ void expand_quarter_row(const uint8_t* raw, uint8_t* dst, int r, int c) {
+  const uint4 w = *reinterpret_cast<const uint4*>(raw + r * kRow8 + ((c ^ ((r >> 1) & 3)) << 4));
+  const uint2 e0 = expand4<T>(w.x), e1 = expand4<T>(w.y), e2 = expand4<T>(w.z), e3 = expand4<T>(w.w);
+  uint8_t* dst_row = dst + r * kRow16;
+  const int sw16 = r & 7;
+  *reinterpret_cast<uint4*>(dst_row + (((2 * c) ^ sw16) << 4)) = make_uint4(e0.x, e0.y, e1.x, e1.y);
+  *reinterpret_cast<uint4*>(dst_row + (((2 * c + 1) ^ sw16) << 4)) = make_uint4(e2.x, e2.y, e3.x, e3.y);
 }
 
 // ------------------------------------------------------------------------ epilogue
