@@ -570,8 +570,12 @@ def run_shape_sweep(args):
 
     results = []
     shapes = [(name, n, k) for name, k, n, _ in PROJECTIONS]
+    want_ops = args.sweep_op.split(",") if args.sweep_op else ["w8a8", "w8a16", "act_quant"]
+    want_m = [int(m) for m in args.sweep_m.split(",")] if args.sweep_m else [1, 16, 128, 512, TOKENS]
     for op in ("w8a8", "w8a16"):
-        for M in (1, 16, 128, 512, TOKENS):
+        if op not in want_ops:
+            continue
+        for M in want_m:
             for name, N, K in shapes:
                 us = time_op(op, M, N, K, 20 if M == TOKENS else 100)
                 in_bytes = M * K * (1 if op == "w8a8" else 2)
@@ -584,6 +588,8 @@ def run_shape_sweep(args):
                                 "path": L.b200q_select_path(_lib.OP_W8A8 if op == "w8a8" else _lib.OP_W8A16,
                                                             M, N, K).decode()})
     for name, N, K in shapes:
+        if "act_quant" not in want_ops:
+            break
         us = time_op("act_quant", TOKENS, N, K, 50)
         b = 3 * TOKENS * K + 4 * TOKENS
         results.append({"op": "act_quant", "proj": name, "M": TOKENS, "K": K, "us": round(us, 2),
@@ -605,6 +611,8 @@ def main():
                          "replaying one CUDA graph per step")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="sum row-parallel outputs with NCCL instead of the peer-memory kernel")
+    ap.add_argument("--sweep-op", default="", help="shape_sweep: comma list of w8a8,w8a16,act_quant")
+    ap.add_argument("--sweep-m", default="", help="shape_sweep: comma list of token counts")
     ap.add_argument("--mode", default="headline", choices=["headline", "shape_sweep"],
                     help="shape_sweep prints per-shape kernel times (decode and prefill shapes)")
     args = ap.parse_args()

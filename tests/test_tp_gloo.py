@@ -44,8 +44,26 @@ def _worker(rank, world, port, out_dir):
         y = down(gate * up)                          # all-reduce inside
         full = torch.nn.functional.linear(x, w_gu)
         ref = torch.nn.functional.linear(full[:, :32] * full[:, 32:], w_down, b_down)
-        torch.save({"ok": bool(torch.allclose(y, ref, atol=1e-3, rtol=1e-4)), "y": y},
-                   os.path.join(out_dir, f"r{rank}.pt"))
+        ok = bool(torch.allclose(y, ref, atol=1e-3, rtol=1e-4))
+
+        # a communicator installed with set_tp_all_reduce takes over the exchange step
+        from tiny_vllm_b200.layers import linear as LL
+
+        class CountingComm:
+            """Stands in for layers.tp_comm.PeerAllReduce: same ``reduce`` contract."""
+            calls = 0
+
+            def reduce(self, t):
+                CountingComm.calls += 1
+                dist.all_reduce(t)
+                return t
+
+        LL.set_tp_all_reduce(CountingComm())
+        y2 = down(gate * up)
+        LL.set_tp_all_reduce(None)
+        y3 = down(gate * up)
+        ok = ok and CountingComm.calls == 1 and torch.equal(y2, y) and torch.equal(y3, y)
+        torch.save({"ok": ok, "y": y}, os.path.join(out_dir, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
 

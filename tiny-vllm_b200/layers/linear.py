@@ -279,7 +279,7 @@ class RowParallelLinear(LinearBase):
             # ``None`` bias lets the quant method pick ``self.bias`` on every rank.
             y = self.quant_method.apply(x, self, bias)
         if self.tp_size > 1:
-            if comm is not None and y.is_cuda:
+            if comm is not None:
                 return comm.reduce(y)
             dist.all_reduce(y)
         return y
