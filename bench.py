@@ -303,7 +303,7 @@ def run_gpu_arm(args):
                 events.append((w["name"], e0, e1))
             if w["split"] == "row" and tp > 1:
                 if comm is not None:
-                    comm.all_reduce_(w["y"])
+                    comm.large_(w["y"])     # pull kernel for two ranks, two-shot beyond
                 else:
                     dist.all_reduce(w["y"])
 
@@ -490,7 +490,7 @@ def run_gpu_arm(args):
                                    "(qkv 1024->4096, o 2048->1024, gate_up 1024->6144, down 3072->1024)",
                        "tokens": TOKENS, "parallelism": f"tp{world}",
                        "allreduce": ("none" if world == 1 else
-                                     "b200q_tp_allreduce (peer memory)" if comm is not None else "nccl"),
+                                     ("b200q_tp_allreduce_pull (peer memory)" if world == 2 else "b200q_tp_allreduce (peer memory)") if comm is not None else "nccl"),
                        "launch": ("one CUDA graph replay per step (act-quant + GEMM x 4, plus the "
                                   "all-reduces at tp > 1)" if step_graph is not None
                                   else "eager launches through the C ABI"),

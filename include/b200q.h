@@ -181,6 +181,21 @@ int b200q_tp_allreduce(void* const* peer_buffers, void* const* peer_flag_pads, i
                        size_t n_elems, int dtype, void* stream);
 
 /*
+ * Pull variant of b200q_tp_allreduce: every rank reads all ranks' buffers over NVLink and
+ * writes the sum (fp32, rank order, bit-identical on all ranks and to b200q_tp_allreduce)
+ * into `out`, an ordinary local tensor that must not alias the rank's own input buffer.
+ * Nothing is written to a peer, so there is no closing barrier: about a third faster than
+ * the two-shot kernel for two ranks, more traffic than it beyond two.  The input buffers
+ * must stay untouched until every peer has read them, which the next call of this function
+ * or of b200q_tp_allreduce on the same flag pads guarantees (a rank announces itself there
+ * only after its own kernel has finished): alternate between two input buffers and keep one
+ * such call between two writes to the same buffer.  Same arguments and limits otherwise;
+ * a wait that runs out sets device status 0x503.
+ */
+int b200q_tp_allreduce_pull(void* const* peer_buffers, void* const* peer_flag_pads, void* out,
+                            int rank, int world, size_t n_elems, int dtype, void* stream);
+
+/*
  * Row-parallel linear for decode-sized batches with the sum over the tensor-parallel ranks
  * fused into the GEMM kernel: replaces the pair "quantized linear, then dist.all_reduce(y)"
  * of RowParallelLinear.forward (nanovllm/layers/linear.py:265-276) by ONE kernel per rank.

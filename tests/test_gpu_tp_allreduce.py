@@ -55,6 +55,26 @@ def _worker(rank, world, port, out_dir):
             ok = ok and same
             if not same:
                 notes.append(f"call {call}: mismatch, max diff {(t.cpu().float() - expect.float()).abs().max()}")
+        # pull variant: sum lands in a new local tensor, inputs alternate between the two slots
+        for call, (n, dtype) in enumerate([(8192 * 1024, torch.bfloat16), (4096, torch.float16),
+                                           (1024 * 1024 + 8, torch.bfloat16), (8, torch.bfloat16),
+                                           (8192 * 1024, torch.bfloat16)]):
+            parts = [_rank_tensor(r, n, 20 + call, dtype) for r in range(world)]
+            expect = torch.zeros(n, dtype=torch.float32)
+            for r in range(world):
+                expect += parts[r].float()
+            expect = expect.to(dtype)
+            t = comm.buffer((n,), dtype)
+            t.copy_(parts[rank])
+            out = comm.all_reduce_pull(t)
+            torch.cuda.synchronize()
+            if not torch.equal(out.cpu().view(torch.int16), expect.view(torch.int16)):
+                ok = False
+                notes.append(f"pull call {call} (n={n}): mismatch")
+            if not torch.equal(t.cpu().view(torch.int16), parts[rank].view(torch.int16)):
+                ok = False
+                notes.append(f"pull call {call}: the input buffer was modified")
+        ok = ok and _lib.lib().b200q_device_status() == 0
         # one-trip kernel for small tensors: any local tensor, in place, same bits
         for call, (n, dtype) in enumerate([(8, torch.bfloat16), (4096, torch.float16),
                                            (16 * 1024, torch.bfloat16), (96 * 1024, torch.bfloat16),
@@ -90,7 +110,15 @@ def _worker(rank, world, port, out_dir):
         # timing against NCCL on the largest message
         t = comm.buffer((8192 * 1024,), torch.bfloat16)
         x = torch.zeros(8192 * 1024, dtype=torch.bfloat16, device="cuda")
-        for fn, name in ((lambda: comm.all_reduce_(t), "peer"), (lambda: dist.all_reduce(x), "nccl")):
+        t2 = comm.buffer((8192 * 1024,), torch.bfloat16)
+        turn = [0]
+
+        def pull_alternating():
+            turn[0] ^= 1
+            comm.all_reduce_pull(t if turn[0] else t2)
+
+        for fn, name in ((lambda: comm.all_reduce_(t), "peer"), (pull_alternating, "peer pull"),
+                         (lambda: dist.all_reduce(x), "nccl")):
             for _ in range(3):
                 fn()
             torch.cuda.synchronize()

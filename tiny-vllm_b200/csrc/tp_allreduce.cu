@@ -126,6 +126,71 @@ tp_allreduce_kernel(const Params p) {
   }
 }
 
+// ---------------------------------------------------------------- pull variant
+// Every rank reads ALL peers' buffers and keeps the sum in a local output tensor: nothing is
+// written to a peer, so there is no fence, no acknowledgement to wait for and no closing
+// barrier.  Each rank receives (world - 1) x the tensor over NVLink, which equals the two-shot
+// scheme's traffic for two ranks (where this variant is used) and exceeds it beyond.
+// The inputs must stay untouched until every peer has read them; that is guaranteed by the
+// NEXT collective on the same flag pad: a rank announces itself there only after its own
+// pull kernel has finished, and nobody passes that announcement barrier without it.  The
+// caller therefore alternates between (at least) two input buffers and runs a kernel of
+// this file between two writes to the same buffer — which a sequence of row-parallel layers
+// does by construction.
+template <bool BF16, int W, int U>
+__global__ void __launch_bounds__(kThreads)
+tp_allreduce_pull_kernel(const Params p, uint4* __restrict__ out) {
+  __shared__ unsigned int s_epoch;
+  __shared__ int s_flag;
+  unsigned int* my_pad = p.pad[p.rank];
+  if (threadIdx.x == 0) {
+    s_epoch = *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) + 1u;
+    s_flag = 0;
+  }
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
+  if (threadIdx.x < p.world) {
+    if (blockIdx.x == 0) st_release_sys(p.pad[threadIdx.x] + kSlotA + p.rank, epoch);
+    if (!wait_flag(my_pad + kSlotA + threadIdx.x, epoch)) s_flag = 1;
+  }
+  __syncthreads();
+  if (s_flag == 0) {
+    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * kThreads;
+    for (unsigned long long i0 = static_cast<unsigned long long>(blockIdx.x) * kThreads + threadIdx.x;
+         i0 < p.n_chunks; i0 += stride * U) {
+      uint4 v[U][W];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const unsigned long long i = i0 + stride * u;
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+          if (r < p.world && i < p.n_chunks) v[u][r] = ld_peer16(static_cast<const uint4*>(p.buf[r]) + i);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const unsigned long long i = i0 + stride * u;
+        if (i >= p.n_chunks) break;
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+          if (r < p.world) accumulate<BF16>(acc, v[u][r]);
+        out[i] = pack<BF16>(acc);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_flag != 0) atomicCAS(p.status, 0, 0x503);
+    // the rank's last CTA publishes the finished call number (the next launch reads it)
+    if (atomicAdd(my_pad + kSlotCounter, 1u) == gridDim.x - 1) {
+      my_pad[kSlotCounter] = 0u;
+      *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- small tensors, one trip
 // For tensors of up to a few hundred kilobytes the two barriers above cost more than the
 // data.  Here every rank pushes its whole tensor to every peer as tagged 8-byte words and
@@ -435,6 +500,57 @@ extern "C" int b200q_tp_allreduce_small(const void* x, void* y, size_t n_elems, 
   } else {
     tp_allreduce_onetrip_kernel<false><<<static_cast<int>(blocks), kThreads, 0, st>>>(p);
   }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  count_launch();
+  return B200Q_OK;
+}
+
+extern "C" int b200q_tp_allreduce_pull(void* const* peer_buffers, void* const* peer_flag_pads,
+                                       void* out, int rank, int world, size_t n_elems, int dtype,
+                                       void* stream) {
+  using namespace b200q;
+  if (peer_buffers == nullptr || peer_flag_pads == nullptr || out == nullptr)
+    return B200Q_ERR_NULL_POINTER;
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return B200Q_ERR_BAD_ARGUMENT;
+  if (dtype != B200Q_DTYPE_F16 && dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  if (n_elems == 0 || (n_elems % 8) != 0) return B200Q_ERR_UNSUPPORTED_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return B200Q_ERR_MISALIGNED;
+  Params p{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_buffers[r] == nullptr || peer_flag_pads[r] == nullptr) return B200Q_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(peer_buffers[r]) & 15u) != 0) return B200Q_ERR_MISALIGNED;
+    p.buf[r] = peer_buffers[r];
+    p.pad[r] = static_cast<unsigned int*>(peer_flag_pads[r]);
+  }
+  if (out == peer_buffers[rank]) return B200Q_ERR_BAD_ARGUMENT;  // peers still read the input
+  if (device_cc_major() != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+  p.rank = rank;
+  p.world = world;
+  p.n_chunks = n_elems / 8;
+  p.is_bf16 = dtype == B200Q_DTYPE_BF16;
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return B200Q_ERR_LAUNCH;
+  long long blocks = static_cast<long long>((p.n_chunks + kThreads * 4 - 1) / (kThreads * 4));
+  if (blocks < 1) blocks = 1;
+  if (blocks > 2 * sm_count()) blocks = 2 * sm_count();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = static_cast<int>(blocks);
+  uint4* o = static_cast<uint4*>(out);
+#define B200Q_PULL_LAUNCH(BF, W, U) tp_allreduce_pull_kernel<BF, W, U><<<grid, kThreads, 0, st>>>(p, o)
+  if (p.is_bf16) {
+    if (world <= 2) B200Q_PULL_LAUNCH(true, 2, 8);
+    else if (world <= 4) B200Q_PULL_LAUNCH(true, 4, 2);
+    else B200Q_PULL_LAUNCH(true, 8, 1);
+  } else {
+    if (world <= 2) B200Q_PULL_LAUNCH(false, 2, 8);
+    else if (world <= 4) B200Q_PULL_LAUNCH(false, 4, 2);
+    else B200Q_PULL_LAUNCH(false, 8, 1);
+  }
+#undef B200Q_PULL_LAUNCH
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     note_cuda_error(e);

@@ -126,6 +126,30 @@ class PeerAllReduce:
         _lib.check(rc, "b200q_tp_allreduce", f"n={t.numel()} world={self.world}")
         return t
 
+    def all_reduce_pull(self, t: torch.Tensor) -> torch.Tensor:
+        """Sums ``t`` (a tensor from :meth:`buffer`) over the group into a NEW local tensor:
+        every rank reads the peers' buffers, nothing is written remotely and no closing
+        barrier is needed.  ``t`` must not be rewritten before the next collective of this
+        communicator on a symmetric slot has run (the rotating slots of :meth:`buffer` and a
+        sequence of row-parallel layers guarantee that)."""
+        if not self.owns(t):
+            raise RuntimeError("all_reduce_pull needs a contiguous tensor obtained from buffer()")
+        if t.dtype not in _DTYPE_IDS or t.numel() % 8 != 0:
+            raise RuntimeError("all_reduce_pull supports fp16/bf16 tensors with a multiple of 8 elements")
+        out = torch.empty_like(t)
+        off = t.data_ptr() - self._data.data_ptr()
+        bufs = (ctypes.c_void_p * self.world)(*[p + off for p in self._data_ptrs])
+        rc = _lib.lib().b200q_tp_allreduce_pull(bufs, self._pad_arr, out.data_ptr(), self.rank,
+                                                self.world, t.numel(), _DTYPE_IDS[t.dtype],
+                                                torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "b200q_tp_allreduce_pull", f"n={t.numel()} world={self.world}")
+        return out
+
+    def large_(self, t: torch.Tensor) -> torch.Tensor:
+        """All-reduce of a tensor that lives in a symmetric slot by the faster of the two
+        large-tensor kernels: pull for two ranks, two-shot beyond."""
+        return self.all_reduce_pull(t) if self.world == 2 else self.all_reduce_(t)
+
     def small_fits(self, t: torch.Tensor) -> bool:
         """True when ``t`` qualifies for the one-trip kernel: 16-bit, contiguous, a multiple of
         8 elements, at most ``small_max_bytes`` and within the receive area."""
@@ -152,10 +176,10 @@ class PeerAllReduce:
         if y.is_cuda and y.dtype in _DTYPE_IDS and y.numel() % 8 == 0 \
                 and y.numel() * y.element_size() <= self.slot_bytes:
             if self.owns(y):
-                return self.all_reduce_(y)
+                return self.large_(y)
             shared = self.buffer(y.shape, y.dtype)
             shared.copy_(y)
-            return self.all_reduce_(shared)
+            return self.large_(shared)
         dist.all_reduce(y, group=self.group)
         return y
 
