@@ -72,6 +72,44 @@ def test_argument_validation_needs_no_device(L):
     assert L.b200q_w8a16_gemm(p, p + 8, p, None, p, 4, 8, 64, 1, None, 0, None) == _lib.ERR_MISALIGNED
 
 
+def test_peer_entry_points_validate_before_touching_a_device(L):
+    buf = ctypes.create_string_buffer(8192 + 512)
+    p = (ctypes.addressof(buf) + 255) & ~255  # 256-byte aligned host address, never dereferenced
+    two = (ctypes.c_void_p * 2)(p, p + 1024)
+    holes = (ctypes.c_void_p * 2)(p, None)
+    odd = (ctypes.c_void_p * 2)(p, p + 1028)
+    # two-shot, pull and one-trip all-reduce
+    assert L.b200q_tp_allreduce(None, two, 0, 2, 64, 1, None) == _lib.ERR_NULL_POINTER
+    assert L.b200q_tp_allreduce(two, two, 2, 2, 64, 1, None) == _lib.ERR_BAD_ARGUMENT
+    assert L.b200q_tp_allreduce(two, two, 0, 9, 64, 1, None) == _lib.ERR_BAD_ARGUMENT
+    assert L.b200q_tp_allreduce(two, two, 0, 2, 60, 1, None) == _lib.ERR_UNSUPPORTED_SHAPE
+    assert L.b200q_tp_allreduce(holes, two, 0, 2, 64, 1, None) == _lib.ERR_NULL_POINTER
+    assert L.b200q_tp_allreduce(odd, two, 0, 2, 64, 1, None) == _lib.ERR_MISALIGNED
+    assert L.b200q_tp_allreduce_pull(two, two, None, 0, 2, 64, 1, None) == _lib.ERR_NULL_POINTER
+    assert L.b200q_tp_allreduce_pull(two, two, p + 2048, 0, 2, 64, 3, None) == _lib.ERR_BAD_ARGUMENT
+    assert L.b200q_tp_allreduce_pull(two, two, p, 0, 2, 64, 1, None) == _lib.ERR_BAD_ARGUMENT  # out aliases input
+    assert L.b200q_tp_allreduce_pull(two, two, p + 2056, 0, 2, 64, 1, None) == _lib.ERR_MISALIGNED
+    assert L.b200q_tp_allreduce_small(p, p, 60, 1, two, two, 4096, 0, 2, None) == _lib.ERR_UNSUPPORTED_SHAPE
+    assert L.b200q_tp_allreduce_small(p, p, 4096, 1, two, two, 4096, 0, 2, None) == _lib.ERR_WORKSPACE
+    assert L.b200q_tp_allreduce_small(p, p, 64, 1, None, two, 4096, 0, 2, None) == _lib.ERR_NULL_POINTER
+    # fused decode GEMM + all-reduce
+    args = (p, p, p, p, None, p)
+    assert L.b200q_w8a8_gemm_allreduce(*args, 16, 64, 64, 1, two, two, 1 << 20, 0, 2, None) in (
+        _lib.ERR_UNSUPPORTED_ARCH, _lib.ERR_LAUNCH)            # arguments fine, no B200 here
+    assert L.b200q_w8a8_gemm_allreduce(*args, 16, 64, 64, 1, None, two, 1 << 20, 0, 2, None) in (
+        _lib.ERR_NULL_POINTER, _lib.ERR_UNSUPPORTED_ARCH, _lib.ERR_LAUNCH)
+    assert L.b200q_w8a8_gemm_allreduce(*args, 16, 64, 24, 1, two, two, 1 << 20, 0, 2, None) == _lib.ERR_UNSUPPORTED_SHAPE
+    assert L.b200q_w8a16_gemm_allreduce(None, p, p, None, p, 16, 64, 64, 1, two, two, 1 << 20, 0, 2,
+                                        None) == _lib.ERR_NULL_POINTER
+    # fused prefill route
+    assert L.b200q_w8a8_gemm_allreduce_tiled(p, p, p, p, None, two, 1000, 64, 64, 1, two, 1 << 20, two, 0,
+                                             2, None) == _lib.ERR_UNSUPPORTED_SHAPE      # M % (2 * 256)
+    assert L.b200q_w8a8_gemm_allreduce_tiled(p, p, p, p, None, two, 1024, 64, 64, 1, two, 1024, two, 0, 2,
+                                             None) == _lib.ERR_WORKSPACE
+    assert L.b200q_w8a8_gemm_allreduce_tiled(p, p, p, p, None, None, 1024, 64, 64, 1, two, 1 << 20, two, 0,
+                                             2, None) == _lib.ERR_NULL_POINTER
+
+
 def test_path_names_and_workspace_queries(L):
     assert L.b200q_select_path(_lib.OP_W8A8, 8192, 4096, 1024) == b"umma_i8_pair_tokens256"
     assert L.b200q_select_path(_lib.OP_W8A8, 300, 4096, 1024) == b"umma_i8_tokens128"
