@@ -181,6 +181,19 @@ int b200q_tp_allreduce(void* const* peer_buffers, void* const* peer_flag_pads, i
                        size_t n_elems, int dtype, void* stream);
 
 /*
+ * b200q_tp_allreduce with the data phase done by the NVSwitch (NVLS): multicast_buffer is the
+ * MULTICAST address of the symmetric tensor (the mapping through which a store reaches every
+ * rank's copy and a reducing load returns the sum of all copies), peer_flag_pads as above.
+ * In place; rank r reduces slice r with multimem.ld_reduce (fp32 accumulation in the
+ * switch) and broadcasts it with multimem.st.  All ranks receive identical bits; the
+ * addition order is the switch's, so the last bit may differ from the rank-ordered sum of
+ * b200q_tp_allreduce.  Less link traffic than the two-shot kernel from four ranks up.
+ * A wait that runs out sets device status 0x504 / 0x505.
+ */
+int b200q_tp_allreduce_multimem(void* multicast_buffer, void* const* peer_flag_pads, int rank,
+                                int world, size_t n_elems, int dtype, void* stream);
+
+/*
  * Pull variant of b200q_tp_allreduce: every rank reads all ranks' buffers over NVLink and
  * writes the sum (fp32, rank order, bit-identical on all ranks and to b200q_tp_allreduce)
  * into `out`, an ordinary local tensor that must not alias the rank's own input buffer.

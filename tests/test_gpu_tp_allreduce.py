@@ -75,6 +75,34 @@ def _worker(rank, world, port, out_dir):
                 ok = False
                 notes.append(f"pull call {call}: the input buffer was modified")
         ok = ok and _lib.lib().b200q_device_status() == 0
+        # in-switch reduction (when the fabric offers a multicast mapping): identical bits on
+        # all ranks, within one unit in the last place of the rank-ordered sum
+        if comm._mc_ptr != 0:
+            for call, (n, dtype) in enumerate([(8192 * 1024, torch.bfloat16), (4096, torch.float16),
+                                               (8, torch.bfloat16), (1024 * 1024 + 8, torch.bfloat16)]):
+                parts = [_rank_tensor(r, n, 70 + call, dtype) for r in range(world)]
+                expect = torch.zeros(n, dtype=torch.float32)
+                for r in range(world):
+                    expect += parts[r].float()
+                expect = expect.to(dtype)
+                t = comm.buffer((n,), dtype)
+                t.copy_(parts[rank])
+                comm.all_reduce_multimem_(t)
+                torch.cuda.synchronize()
+                got = t.cpu()
+                ulp = (got.view(torch.int16).int() - expect.view(torch.int16).int()).abs()
+                if int(ulp.max()) > 1:
+                    ok = False
+                    notes.append(f"multimem call {call} (n={n}): off by {int(ulp.max())} units in the last place")
+                gathered = [torch.empty_like(t) for _ in range(world)]
+                dist.all_gather(gathered, t)
+                if not all(torch.equal(g.view(torch.int16), t.view(torch.int16)) for g in gathered):
+                    ok = False
+                    notes.append(f"multimem call {call}: ranks disagree")
+            notes.append("multicast mapping available")
+        else:
+            notes.append("no multicast mapping: in-switch reduction not tested")
+        ok = ok and _lib.lib().b200q_device_status() == 0
         # one-trip kernel for small tensors: any local tensor, in place, same bits
         for call, (n, dtype) in enumerate([(8, torch.bfloat16), (4096, torch.float16),
                                            (16 * 1024, torch.bfloat16), (96 * 1024, torch.bfloat16),
@@ -117,8 +145,11 @@ def _worker(rank, world, port, out_dir):
             turn[0] ^= 1
             comm.all_reduce_pull(t if turn[0] else t2)
 
-        for fn, name in ((lambda: comm.all_reduce_(t), "peer"), (pull_alternating, "peer pull"),
-                         (lambda: dist.all_reduce(x), "nccl")):
+        routes = [(lambda: comm.all_reduce_(t), "peer"), (pull_alternating, "peer pull"),
+                  (lambda: dist.all_reduce(x), "nccl")]
+        if comm._mc_ptr != 0:
+            routes.insert(2, (lambda: comm.all_reduce_multimem_(t), "peer multimem"))
+        for fn, name in routes:
             for _ in range(3):
                 fn()
             torch.cuda.synchronize()

@@ -75,6 +75,8 @@ SIGNATURES = {
                                                    _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
                                                    _c.c_int, _c.c_int, _c.c_void_p, _c.c_size_t,
                                                    _c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p]),
+    "b200q_tp_allreduce_multimem": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
+                                               _c.c_size_t, _c.c_int, _c.c_void_p]),
     "b200q_tp_allreduce_pull": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
                                            _c.c_size_t, _c.c_int, _c.c_void_p]),
     "b200q_tp_allreduce_small": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int,

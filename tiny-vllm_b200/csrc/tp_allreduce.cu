@@ -126,6 +126,102 @@ tp_allreduce_kernel(const Params p) {
   }
 }
 
+// ---------------------------------------------------------------- in-switch reduction
+// Same two barriers as the two-shot kernel, but the data phase runs through the NVSwitch's
+// multicast/reduction engine (NVLS): one multimem.ld_reduce on the multicast address returns
+// the sum of all ranks' values for 16 bytes (fp32 accumulation inside the switch), one
+// multimem.st writes the result into every rank's buffer.  Rank r handles slice r.  A GPU
+// sends each of its bytes once and receives the full result once, instead of sending and
+// receiving (world - 1) / world of the tensor twice: less link traffic from four ranks up.
+// All ranks end up with identical bits (one reduction per element, broadcast), but the
+// order of the fp32 additions is the switch's, so a result can differ from the rank-ordered
+// sum of the other kernels in the last bit.  Plain multimem loads/stores on a multicast
+// mapping; no TMA.
+template <bool BF16>
+__device__ __forceinline__ uint4 multimem_ld_reduce16(const void* mc) {
+  uint4 v;
+  if (BF16) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+  } else {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+  }
+  return v;
+}
+__device__ __forceinline__ void multimem_st16(void* mc, const uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+template <bool BF16, int U>
+__global__ void __launch_bounds__(kThreads)
+tp_allreduce_multimem_kernel(const Params p, uint4* __restrict__ mc) {
+  __shared__ unsigned int s_epoch;
+  __shared__ int s_flag;  // 0 ok, 1 = a wait gave up, 2 = this CTA is the rank's last
+  unsigned int* my_pad = p.pad[p.rank];
+  if (threadIdx.x == 0) {
+    s_epoch = *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) + 1u;
+    s_flag = 0;
+  }
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
+  if (threadIdx.x < p.world) {
+    if (blockIdx.x == 0) st_release_sys(p.pad[threadIdx.x] + kSlotA + p.rank, epoch);
+    if (!wait_flag(my_pad + kSlotA + threadIdx.x, epoch)) s_flag = 1;
+  }
+  __syncthreads();
+  if (s_flag == 0) {
+    const unsigned long long per_rank = (p.n_chunks + p.world - 1) / p.world;
+    const unsigned long long begin = per_rank * p.rank;
+    const unsigned long long end = min(p.n_chunks, begin + per_rank);
+    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * kThreads;
+    for (unsigned long long i0 = begin + static_cast<unsigned long long>(blockIdx.x) * kThreads +
+                                 threadIdx.x;
+         i0 < end; i0 += stride * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const unsigned long long i = i0 + stride * u;
+        if (i < end) v[u] = multimem_ld_reduce16<BF16>(mc + i);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const unsigned long long i = i0 + stride * u;
+        if (i < end) multimem_st16(mc + i, v[u]);
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(my_pad + kSlotCounter, 1u);
+    if (done == gridDim.x - 1) {
+      my_pad[kSlotCounter] = 0u;
+      if (s_flag == 0) s_flag = 2;
+    }
+  }
+  __syncthreads();
+  if (s_flag == 2) {
+    __threadfence_system();
+    if (threadIdx.x < p.world) {
+      st_release_sys(p.pad[threadIdx.x] + kSlotB + p.rank, epoch);
+      if (!wait_flag(my_pad + kSlotB + threadIdx.x, epoch)) atomicCAS(p.status, 0, 0x505);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
+  } else if (s_flag == 1 && threadIdx.x == 0) {
+    atomicCAS(p.status, 0, 0x504);
+    if (blockIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
+  }
+}
+
 // ---------------------------------------------------------------- pull variant
 // Every rank reads ALL peers' buffers and keeps the sum in a local output tensor: nothing is
 // written to a peer, so there is no fence, no acknowledgement to wait for and no closing
@@ -551,6 +647,47 @@ extern "C" int b200q_tp_allreduce_pull(void* const* peer_buffers, void* const* p
     else B200Q_PULL_LAUNCH(false, 8, 1);
   }
 #undef B200Q_PULL_LAUNCH
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    note_cuda_error(e);
+    return B200Q_ERR_LAUNCH;
+  }
+  count_launch();
+  return B200Q_OK;
+}
+
+extern "C" int b200q_tp_allreduce_multimem(void* multicast_buffer, void* const* peer_flag_pads,
+                                           int rank, int world, size_t n_elems, int dtype,
+                                           void* stream) {
+  using namespace b200q;
+  if (multicast_buffer == nullptr || peer_flag_pads == nullptr) return B200Q_ERR_NULL_POINTER;
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return B200Q_ERR_BAD_ARGUMENT;
+  if (dtype != B200Q_DTYPE_F16 && dtype != B200Q_DTYPE_BF16) return B200Q_ERR_BAD_ARGUMENT;
+  if (n_elems == 0 || (n_elems % 8) != 0) return B200Q_ERR_UNSUPPORTED_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(multicast_buffer) & 15u) != 0) return B200Q_ERR_MISALIGNED;
+  Params p{};
+  for (int r = 0; r < world; ++r) {
+    if (peer_flag_pads[r] == nullptr) return B200Q_ERR_NULL_POINTER;
+    p.pad[r] = static_cast<unsigned int*>(peer_flag_pads[r]);
+  }
+  if (device_cc_major() != 10) return B200Q_ERR_UNSUPPORTED_ARCH;
+  p.rank = rank;
+  p.world = world;
+  p.n_chunks = n_elems / 8;
+  p.is_bf16 = dtype == B200Q_DTYPE_BF16;
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return B200Q_ERR_LAUNCH;
+  const unsigned long long per_rank = (p.n_chunks + world - 1) / world;
+  long long blocks = static_cast<long long>((per_rank + kThreads * 4 - 1) / (kThreads * 4));
+  if (blocks < 1) blocks = 1;
+  if (blocks > sm_count()) blocks = sm_count();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint4* mc = static_cast<uint4*>(multicast_buffer);
+  if (p.is_bf16) {
+    tp_allreduce_multimem_kernel<true, 4><<<static_cast<int>(blocks), kThreads, 0, st>>>(p, mc);
+  } else {
+    tp_allreduce_multimem_kernel<false, 4><<<static_cast<int>(blocks), kThreads, 0, st>>>(p, mc);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     note_cuda_error(e);

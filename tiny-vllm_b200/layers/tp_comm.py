@@ -84,6 +84,10 @@ class PeerAllReduce:
         torch.cuda.synchronize()
         dist.barrier(self.group)           # every pad is zero before anyone signals
         self._data_ptrs = [int(p) for p in self._data_hdl.buffer_ptrs]
+        # multicast mapping of the data buffer (0 when the fabric offers none): in-switch sums
+        self._mc_ptr = int(getattr(self._data_hdl, "multicast_ptr", 0) or 0)
+        self.use_multimem = (self._mc_ptr != 0 and self.world >= 4
+                             and os.environ.get("B200Q_MULTIMEM_ALLREDUCE", "0") == "1")
         pads = [int(p) for p in self._pad_hdl.buffer_ptrs]
         self._pad_arr = (ctypes.c_void_p * self.world)(*pads)
         self._recv_arr = (ctypes.c_void_p * self.world)(*[int(p) for p in self._recv_hdl.buffer_ptrs])
@@ -145,10 +149,32 @@ class PeerAllReduce:
         _lib.check(rc, "b200q_tp_allreduce_pull", f"n={t.numel()} world={self.world}")
         return out
 
+    def all_reduce_multimem_(self, t: torch.Tensor) -> torch.Tensor:
+        """In-place sum of a tensor from :meth:`buffer` through the NVSwitch's reduction engine
+        (needs a multicast mapping).  Same bits on every rank; the addition order is the
+        switch's, so the last bit can differ from :meth:`all_reduce_`."""
+        if self._mc_ptr == 0:
+            raise RuntimeError("no multicast mapping for the symmetric buffer on this system")
+        if not self.owns(t):
+            raise RuntimeError("all_reduce_multimem_ needs a contiguous tensor obtained from buffer()")
+        if t.dtype not in _DTYPE_IDS or t.numel() % 8 != 0:
+            raise RuntimeError("all_reduce_multimem_ supports fp16/bf16 tensors with a multiple of 8 elements")
+        off = t.data_ptr() - self._data.data_ptr()
+        rc = _lib.lib().b200q_tp_allreduce_multimem(self._mc_ptr + off, self._pad_arr, self.rank,
+                                                    self.world, t.numel(), _DTYPE_IDS[t.dtype],
+                                                    torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "b200q_tp_allreduce_multimem", f"n={t.numel()} world={self.world}")
+        return t
+
     def large_(self, t: torch.Tensor) -> torch.Tensor:
-        """All-reduce of a tensor that lives in a symmetric slot by the faster of the two
-        large-tensor kernels: pull for two ranks, two-shot beyond."""
-        return self.all_reduce_pull(t) if self.world == 2 else self.all_reduce_(t)
+        """All-reduce of a tensor that lives in a symmetric slot by the fastest large-tensor
+        kernel: pull for two ranks, in-switch reduction from four ranks up where a multicast
+        mapping exists, two-shot otherwise."""
+        if self.world == 2:
+            return self.all_reduce_pull(t)
+        if self.use_multimem:
+            return self.all_reduce_multimem_(t)
+        return self.all_reduce_(t)
 
     def small_fits(self, t: torch.Tensor) -> bool:
         """True when ``t`` qualifies for the one-trip kernel: 16-bit, contiguous, a multiple of
