@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import quant_linear_oracle as O
-from gpu_util import device_status_ok, forced_path
+from gpu_util import bits, device_status_ok, forced_path
 from tiny_vllm_b200.quantization.cuda import apply_int8_weight_only_linear
 
 pytestmark = pytest.mark.gpu
@@ -118,6 +118,27 @@ def test_qwen3_8b_shapes(M, N, K):
     assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
     m = O.tensor_metrics(O.w8a16_dequant_matmul(x, q, s), y)
     assert m["relative_l2"] <= 1e-2 and m["cosine_similarity"] >= 0.9999, m
+    assert device_status_ok()
+
+
+@pytest.mark.parametrize("M,N,K,dtype,bias", [(128, 1024, 2048, torch.bfloat16, False),
+                                              (300, 1024, 3072, torch.bfloat16, True),
+                                              (200, 1000, 1040, torch.float16, True),
+                                              (256, 4096, 1024, torch.bfloat16, False)])
+def test_cluster_split_k(M, N, K, dtype, bias, monkeypatch):
+    # decode batches of 64-512 tokens: K is split over a cluster of 2 or 4 CTAs and the leader
+    # adds the peers' partial tiles from its shared memory; ragged M, N and a K tail included
+    q, s = O.make_weight(N, K, seed=N + K)
+    x = O.make_activation(M, K, seed=M, dtype=dtype, outliers=False)
+    b = (torch.randn(N, generator=torch.Generator().manual_seed(2)) * 0.1).to(dtype) if bias else None
+    args = (x.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda())
+    y = apply_int8_weight_only_linear(*args)
+    m = O.tensor_metrics(O.w8a16_native_reference(x, q, s, b), y)
+    assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
+    assert torch.equal(bits(y), bits(apply_int8_weight_only_linear(*args)))     # deterministic
+    monkeypatch.setenv("B200Q_DEBUG_CLUSTER", "1")                              # same kernel, no cluster
+    y1 = apply_int8_weight_only_linear(*args)
+    assert O.tensor_metrics(y1, y)["relative_l2"] <= 2e-3
     assert device_status_ok()
 
 

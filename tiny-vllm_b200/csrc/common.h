@@ -40,6 +40,8 @@ struct UmmaPlan {
   int kb_per_split;
   int stages;        // shared-memory ring depth
   int conv_bufs;     // W8A16 only: ring depth of the converted (16-bit) weight tiles
+  int cluster;       // W8A16 only: CTAs per cluster that split K and reduce through shared memory (1 = off)
+  int partial_bytes; // W8A16 only: shared memory for the partial tiles the cluster leader receives
   int tmem_cols;     // power of two >= 2 * bn
   int grid;          // CTAs launched (persistent)
   size_t smem_bytes;
@@ -104,19 +106,32 @@ int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan);
 // before their first access to global memory.  B200Q_NO_PDL=1 turns the overlap off.
 bool pdl_enabled();
 template <typename... KArgs, typename... Args>
-cudaError_t launch_maybe_overlapped(bool overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block,
-                                    size_t smem, cudaStream_t stream, Args&&... args) {
+cudaError_t launch_clustered(int cluster, bool overlap, void (*kernel)(KArgs...), dim3 grid,
+                             dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = (overlap && pdl_enabled()) ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (cluster > 1) {  // grid.x must be a multiple of the cluster size
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = static_cast<unsigned int>(cluster);
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_maybe_overlapped(bool overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                    size_t smem, cudaStream_t stream, Args&&... args) {
+  return launch_clustered(1, overlap, kernel, grid, block, smem, stream,
+                          static_cast<Args&&>(args)...);
 }
 template <typename... KArgs, typename... Args>
 cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

@@ -38,7 +38,8 @@ namespace {
 
 // 448 threads run; the bound of 512 keeps the kernel at 128 registers per thread, which is
 // what four warps per scheduler can hold.
-template <typename T>
+// CLUSTER: K split over a cluster of p.cluster CTAs, reduced in the leader's shared memory.
+template <typename T, bool CLUSTER>
 __global__ void __launch_bounds__(512, 1)
 w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
                   const __grid_constant__ CUtensorMap tmap_w, const KernelParams p) {
@@ -51,7 +52,8 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint32_t stage_bytes = tile16_bytes + raw_bytes;
   const uint32_t conv_bytes = rows8 * kRow16;
   uint8_t* conv_base = smem + static_cast<size_t>(p.stages) * stage_bytes;
-  uint8_t* staging = conv_base + p.conv_bufs * conv_bytes;
+  float* partial = reinterpret_cast<float*>(conv_base + p.conv_bufs * conv_bytes);  // cluster leader
+  uint8_t* staging = reinterpret_cast<uint8_t*>(partial) + p.partial_bytes;
   float* s_ws = reinterpret_cast<float*>(staging + kStagingBytes);
   uint8_t* ctrl = reinterpret_cast<uint8_t*>(s_ws) + kScaleSmemBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
@@ -60,7 +62,8 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
   uint64_t* cempty_bar = cfull_bar + kMaxConvBufs;  // [conv_bufs] converted tile consumed
   uint64_t* tfull_bar = cempty_bar + kMaxConvBufs;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* pfull_bar = tempty_bar + 2;             // cluster leader: partial tiles have arrived
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pfull_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
 
@@ -85,6 +88,7 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
       ptx::mbar_init(ptx::smem_u32(tfull_bar + b), 1);
       ptx::mbar_init(ptx::smem_u32(tempty_bar + b), kEpiThreads);
     }
+    ptx::mbar_init(ptx::smem_u32(pfull_bar), static_cast<uint32_t>(max(1, p.cluster - 1) * kEpiThreads));
     *abort_flag = 0;
     last_flag[0] = 0;
     last_flag[1] = 0;
@@ -98,6 +102,9 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
+  // the leader's barrier and partial-tile area exist before a peer CTA writes to them
+  constexpr bool clustered = CLUSTER;
+  if (clustered) ptx::cluster_sync_all();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   // everything above overlapped the previous kernel's tail; its results are needed from here
@@ -248,8 +255,30 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int tile_b = t / p.tiles_a;
       const int buf = it & 1;
       const uint32_t tphase = static_cast<uint32_t>(it >> 1) & 1u;
-      const bool fast = p.fast_store && p.splits == 1;
+      const bool fast = p.fast_store && (p.splits == 1 || clustered);
       float* ws_tile = s_ws + buf * 256;
+      if (clustered && split > 0) {
+        // K split over the cluster: hand this CTA's partial tile to the leader (cluster rank
+        // 0 = split 0) through its shared memory, laid out [split - 1][column][row]
+        if (!ptx::mbar_wait(ptx::smem_u32(tfull_bar + buf), tphase, abort_flag)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t taddr_p = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                 static_cast<uint32_t>(buf * p.bn);
+        const uint32_t dst0 = ptx::map_to_cta(ptx::smem_u32(partial), 0) +
+                              (static_cast<uint32_t>((split - 1) * p.bn) * kTileA + row_in_tile) * 4u;
+        for (int c = 0; c < n_chunks_tile; ++c) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(taddr_p + c * 32, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            ptx::st_shared_cluster_u32(dst0 + static_cast<uint32_t>(c * 32 + j) * (kTileA * 4u), v[j]);
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(ptx::smem_u32(tempty_bar + buf));
+        ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(pfull_bar), 0));  // release: stores first
+        continue;
+      }
       if (fast) {
         for (int i = epi_tid; i < p.bn; i += kEpiThreads) {
           const int col = tile_b * p.bn + i;
@@ -258,15 +287,25 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
         ptx::named_bar_sync(2, kEpiThreads);
       }
       if (!ptx::mbar_wait(ptx::smem_u32(tfull_bar + buf), tphase, abort_flag)) break;
+      if (clustered && !ptx::mbar_wait_cluster(ptx::smem_u32(pfull_bar), 0u, abort_flag)) break;
       ptx::tc_fence_after_sync();
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * p.bn);
+      // leader of a cluster: add the peers' partial tiles, in split order (deterministic)
+      auto add_partials = [&](int c0, uint32_t (&v)[32]) {
+        for (int sp = 1; sp < p.cluster; ++sp) {
+          const float* src = partial + static_cast<size_t>((sp - 1) * p.bn + c0) * kTileA + row_in_tile;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), src[j * kTileA]));
+        }
+      };
       float* mine = nullptr;
-      if (p.splits > 1)
+      if (p.splits > 1 && !clustered)
         mine = p.partials + (static_cast<size_t>(t) * p.splits + split) * p.bn * kTileA + row_in_tile;
 
       auto consume = [&](int c0, const uint32_t (&v)[32]) {
-        if (p.splits > 1) {
+        if (p.splits > 1 && !clustered) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             __stcg(mine + static_cast<size_t>(c0 + j) * kTileA, __uint_as_float(v[j]));
@@ -289,6 +328,10 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (p.debug_flags & 1) {
           if (g + 1 < n_groups) issue(g + 1);
           continue;
+        }
+        if (clustered) {
+          add_partials(c * 32, va);
+          if (two) add_partials(c * 32 + 32, vb);
         }
         if (fast) {
           const int row0 = tile_a * kTileA + quarter * 32;
@@ -313,7 +356,7 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(ptx::smem_u32(tempty_bar + buf));
 
-      if (p.splits > 1) {
+      if (p.splits > 1 && !clustered) {
         __threadfence();
         ptx::named_bar_sync(1, kEpiThreads);
         if (epi_tid == 0) {
@@ -352,6 +395,8 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
   __syncwarp();
   ptx::tc_fence_before_sync();
   __syncthreads();
+  // no CTA of a cluster leaves while a peer may still write its shared memory or barriers
+  if (clustered) ptx::cluster_sync_all();
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
@@ -363,19 +408,20 @@ w8a16_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-template <typename T>
+template <typename T, bool CLUSTER>
 cudaError_t launch_kernel(const CUtensorMap& tx, const CUtensorMap& tw, const KernelParams& kp,
                           const UmmaPlan& plan, cudaStream_t stream) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = w8a16_umma_kernel<T>;
+  auto kern = w8a16_umma_kernel<T, CLUSTER>;
   if (dev < 64 && !attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  return launch_overlapped(kern, plan.grid, kThreads, plan.smem_bytes, stream, tx, tw, kp);
+  return launch_clustered(plan.cluster, true, kern, plan.grid, kThreads, plan.smem_bytes, stream, tx,
+                          tw, kp);
 }
 
 }  // namespace
@@ -423,14 +469,38 @@ bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan) {
   if (splits > pl.k_blocks) splits = pl.k_blocks;
   pl.kb_per_split = (pl.k_blocks + splits - 1) / splits;
   pl.splits = (pl.k_blocks + pl.kb_per_split - 1) / pl.kb_per_split;
-  if (pl.splits > 1 && tiles * sizeof(unsigned int) > kCounterBytes) return false;
+  // Few tiles with a long K loop (decode batches of 64-512 tokens on the narrow projections):
+  // a cluster of 2 or 4 CTAs splits K and the leader adds the peers' partial tiles from its own
+  // shared memory — no trip through global memory, unlike the split above.
+  pl.cluster = 1;
+  pl.partial_bytes = 0;
+  if (!swap && pl.splits == 1 && (N % 8) == 0 && (bn % 64) == 0) {
+    int cl = 1;
+    for (int cand : {4, 2})
+      if (tiles * cand <= sms && pl.k_blocks / cand >= 4) {
+        cl = cand;
+        break;
+      }
+    cl = env_int("B200Q_DEBUG_CLUSTER", cl);
+    if (cl == 2 || cl == 4) {
+      const int per = (pl.k_blocks + cl - 1) / cl;
+      if (tiles * cl <= sms && per * (cl - 1) < pl.k_blocks) {
+        pl.cluster = cl;
+        pl.splits = cl;
+        pl.kb_per_split = per;
+        pl.partial_bytes = (cl - 1) * bn * kTileA * static_cast<int>(sizeof(float));
+      }
+    }
+  }
+  if (pl.splits > 1 && pl.cluster == 1 && tiles * sizeof(unsigned int) > kCounterBytes) return false;
   const int rows16 = swap ? bn : kTileA;
   const int rows8 = swap ? kTileA : bn;
   const int stage_bytes = rows16 * kRow16 + rows8 * kRow8;
   // deeper ring of converted tiles where they are small: the expand -> MMA -> release chain
   // takes about a microsecond per K block, so two buffers cap a narrow tile at 0.5 us per block
   pl.conv_bufs = rows8 <= 64 ? 8 : rows8 <= 128 ? 4 : 2;
-  const int fixed = pl.conv_bufs * rows8 * kRow16 + kStagingBytes + kScaleSmemBytes + kCtrlBytes;
+  const int fixed = pl.conv_bufs * rows8 * kRow16 + pl.partial_bytes + kStagingBytes + kScaleSmemBytes +
+                    kCtrlBytes;
   int stages = (kMaxSmem - fixed) / stage_bytes;
   stages = std::min(stages, kMaxStages);
   stages = std::min(stages, std::max(2, pl.kb_per_split));
@@ -442,7 +512,7 @@ bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan) {
   pl.tmem_cols = cols;
   const long long items = tiles * pl.splits;
   pl.grid = static_cast<int>(std::min<long long>(items, sms));
-  pl.ws_bytes = pl.splits > 1
+  pl.ws_bytes = (pl.splits > 1 && pl.cluster == 1)
                     ? kCounterBytes + static_cast<size_t>(tiles) * pl.splits * bn * kTileA * sizeof(float)
                     : 0;
   *plan = pl;
@@ -472,6 +542,8 @@ int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan) {
   kp.kb_per_split = plan.kb_per_split;
   kp.stages = plan.stages;
   kp.conv_bufs = plan.conv_bufs;
+  kp.cluster = plan.cluster;
+  kp.partial_bytes = plan.partial_bytes;
   kp.tmem_cols = plan.tmem_cols;
   kp.swap = plan.swap;
   kp.n_channels = a.N;
@@ -484,12 +556,18 @@ int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan) {
                     ? reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + kCounterBytes)
                     : nullptr;
   kp.status = a.status;
-  kp.fast_store = (!plan.swap && plan.splits == 1 && (a.N % 8) == 0 && (plan.bn % 64) == 0) ? 1 : 0;
+  kp.fast_store = (!plan.swap && (plan.splits == 1 || plan.cluster > 1) && (a.N % 8) == 0 &&
+                   (plan.bn % 64) == 0) ? 1 : 0;
   kp.debug_flags = env_int("B200Q_DEBUG_FLAGS", 0);
 
-  cudaError_t e = a.dtype == B200Q_DTYPE_BF16
-                      ? launch_kernel<__nv_bfloat16>(tx, tw, kp, plan, a.stream)
-                      : launch_kernel<__half>(tx, tw, kp, plan, a.stream);
+  cudaError_t e;
+  if (plan.cluster > 1) {
+    e = a.dtype == B200Q_DTYPE_BF16 ? launch_kernel<__nv_bfloat16, true>(tx, tw, kp, plan, a.stream)
+                                    : launch_kernel<__half, true>(tx, tw, kp, plan, a.stream);
+  } else {
+    e = a.dtype == B200Q_DTYPE_BF16 ? launch_kernel<__nv_bfloat16, false>(tx, tw, kp, plan, a.stream)
+                                    : launch_kernel<__half, false>(tx, tw, kp, plan, a.stream);
+  }
   if (e != cudaSuccess) {
     note_cuda_error(e);
     return B200Q_ERR_LAUNCH;

@@ -216,6 +216,39 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
                : "memory");
 }
 
+// 32-bit store into the shared memory of another CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
+// mbar_wait for a barrier on which other CTAs of the cluster arrive after writing this
+// CTA's shared memory: the acquire has cluster scope, so those writes are visible afterwards.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag) {
+  const long long t0 = clock64();
+  uint32_t it = 0;
+  while (true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok != 0) return true;
+    if ((++it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
 // TMA load into this CTA's shared memory whose completion is counted on an mbarrier of
 // the pair's leader CTA (cluster address).  No data is shared between CTAs by this copy.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* tmap,

@@ -36,6 +36,8 @@ struct KernelParams {
   int k_blocks, splits, kb_per_split;
   int stages;
   int conv_bufs;
+  int cluster;        // CTAs per cluster splitting K (1 = off); split index = cluster rank
+  int partial_bytes;  // shared memory the cluster leader receives partial tiles in
   int tmem_cols;
   int swap;
   int n_channels;
