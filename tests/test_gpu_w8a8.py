@@ -152,6 +152,26 @@ def test_baseline_decode_shapes(M, N, K, oracle_c_lib):
     assert device_status_ok()
 
 
+@pytest.mark.parametrize("M,N,K,dtype,bias", [(128, 1024, 2048, torch.bfloat16, False),
+                                              (300, 1024, 3072, torch.bfloat16, True),
+                                              (200, 1000, 1040, torch.float16, True),
+                                              (100, 1000, 400, torch.bfloat16, False),
+                                              (256, 4096, 1024, torch.bfloat16, False)])
+def test_cluster_split_k(M, N, K, dtype, bias, monkeypatch, oracle_c_lib):
+    # decode batches of 64-512 tokens: K is split over a cluster of 2 or 4 CTAs and the leader
+    # adds the peers' int32 partial tiles from its shared memory: exact, so nothing may change
+    x, xq, a_s, q, s, b = problem(M, N, K, seed=M + K, dtype=dtype, bias=bias)
+    dev = [t.cuda() for t in (xq, a_s, q, s)]
+    bd = None if b is None else b.cuda()
+    ref_acc = O.w8a8_int32_accumulators(xq, q)
+    assert torch.equal(w8a8_int32_accumulators(dev[0], dev[2]).cpu(), ref_acc)
+    y = apply_w8a8_linear(*dev, bias=bd, out_dtype=dtype)
+    assert torch.equal(bits(y.cpu()), bits(O.w8a8_native_epilogue(ref_acc, a_s, s, b, dtype)))
+    monkeypatch.setenv("B200Q_DEBUG_CLUSTER", "1")          # the same kernel without the cluster
+    assert torch.equal(bits(apply_w8a8_linear(*dev, bias=bd, out_dtype=dtype)), bits(y))
+    assert device_status_ok()
+
+
 @pytest.mark.parametrize("M", [16, 300])
 @pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 12288)])
 def test_qwen3_8b_shapes(M, N, K, oracle_c_lib):

@@ -40,8 +40,8 @@ struct UmmaPlan {
   int kb_per_split;
   int stages;        // shared-memory ring depth
   int conv_bufs;     // W8A16 only: ring depth of the converted (16-bit) weight tiles
-  int cluster;       // W8A16 only: CTAs per cluster that split K and reduce through shared memory (1 = off)
-  int partial_bytes; // W8A16 only: shared memory for the partial tiles the cluster leader receives
+  int cluster;       // CTAs per cluster that split K and reduce through shared memory (1 = off)
+  int partial_bytes; // shared memory for the partial tiles the cluster leader receives
   int tmem_cols;     // power of two >= 2 * bn
   int grid;          // CTAs launched (persistent)
   size_t smem_bytes;

@@ -33,7 +33,8 @@
 namespace b200q {
 namespace {
 
-template <typename OutT, int MODE>
+// CLUSTER: K split over a cluster of p.cluster CTAs, reduced in the leader's shared memory.
+template <typename OutT, int MODE, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b, const KernelParams p) {
@@ -41,14 +42,16 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // such a boundary (checked below, the kernel refuses to run otherwise).
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t stage_bytes = kTileA * kBlockK + p.bn * kBlockK;
-  uint8_t* staging = smem + static_cast<size_t>(p.stages) * stage_bytes;
+  int32_t* partial = reinterpret_cast<int32_t*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+  uint8_t* staging = reinterpret_cast<uint8_t*>(partial) + p.partial_bytes;
   float* s_ws = reinterpret_cast<float*>(staging + kStagingBytes);
   uint8_t* ctrl = reinterpret_cast<uint8_t*>(s_ws) + kScaleSmemBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* tfull_bar = empty_bar + kMaxStages;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* pfull_bar = tempty_bar + 2;  // cluster leader: partial tiles have arrived
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pfull_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
 
@@ -69,6 +72,7 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::mbar_init(ptx::smem_u32(tfull_bar + b), 1);
       ptx::mbar_init(ptx::smem_u32(tempty_bar + b), kEpiThreads);
     }
+    ptx::mbar_init(ptx::smem_u32(pfull_bar), static_cast<uint32_t>(max(1, p.cluster - 1) * kEpiThreads));
     *abort_flag = 0;
     last_flag[0] = 0;
     last_flag[1] = 0;
@@ -82,6 +86,9 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
+  // the leader's barrier and partial-tile area exist before a peer CTA writes to them
+  constexpr bool clustered = CLUSTER;
+  if (clustered) ptx::cluster_sync_all();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   // everything above overlapped the previous kernel's tail; its results are needed from here
@@ -185,9 +192,34 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int tile_b = t / p.tiles_a;
       const int buf = it & 1;
       const uint32_t tphase = static_cast<uint32_t>(it >> 1) & 1u;
-      const bool fast = p.fast_store && p.splits == 1;
+      const bool fast = p.fast_store && (p.splits == 1 || clustered);
       float a_s = 0.f;
       float* ws_tile = s_ws + buf * 256;
+      if (clustered && split > 0) {
+        // K split over the cluster: hand this CTA's partial tile (exact int32 sums) to the
+        // leader (cluster rank 0 = split 0) through its shared memory, [split - 1][column][row]
+        if (!ptx::mbar_wait(ptx::smem_u32(tfull_bar + buf), tphase, abort_flag)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t taddr_p = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                 static_cast<uint32_t>(buf * p.bn);
+        const uint32_t dst0 = ptx::map_to_cta(ptx::smem_u32(partial), 0) +
+                              (static_cast<uint32_t>((split - 1) * p.bn) * kTileA + row_in_tile) * 4u;
+        for (int c = half * 2; c < n_chunks_tile; c += 4) {   // this warp's 64-column groups
+          for (int h = 0; h < 2 && c + h < n_chunks_tile; ++h) {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32b_x32(taddr_p + (c + h) * 32, v);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              ptx::st_shared_cluster_u32(dst0 + static_cast<uint32_t>((c + h) * 32 + j) * (kTileA * 4u),
+                                         v[j]);
+          }
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(ptx::smem_u32(tempty_bar + buf));
+        ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(pfull_bar), 0));  // release: stores first
+        continue;
+      }
       if (fast && !(p.debug_flags & 8)) {
         // channel scales of this tile -> shared memory (while the main loop still runs)
         const int col = tile_b * p.bn + epi_tid;
@@ -197,16 +229,25 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
         ptx::named_bar_sync(2, kEpiThreads);
       }
       if (!ptx::mbar_wait(ptx::smem_u32(tfull_bar + buf), tphase, abort_flag)) break;
+      if (clustered && !ptx::mbar_wait_cluster(ptx::smem_u32(pfull_bar), 0u, abort_flag)) break;
       ptx::tc_fence_after_sync();
       const uint32_t taddr =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * p.bn);
+      // leader of a cluster: add the peers' partial tiles (int32: exact in any order)
+      auto add_partials = [&](int c0, uint32_t (&v)[32]) {
+        for (int sp = 1; sp < p.cluster; ++sp) {
+          const int32_t* src = partial + static_cast<size_t>((sp - 1) * p.bn + c0) * kTileA + row_in_tile;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += static_cast<uint32_t>(src[j * kTileA]);
+        }
+      };
       int32_t* mine = nullptr;
-      if (p.splits > 1)
+      if (p.splits > 1 && !clustered)
         mine = p.partials + (static_cast<size_t>(t) * p.splits + split) * p.bn * kTileA + row_in_tile;
 
       // One 32-column chunk in registers -> its destination (generic paths).
       auto consume = [&](int c0, const uint32_t (&v)[32]) {
-        if (p.splits > 1) {
+        if (p.splits > 1 && !clustered) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             __stcg(mine + static_cast<size_t>(c0 + j) * kTileA, static_cast<int32_t>(v[j]));
@@ -238,6 +279,10 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (g + 1 < my_groups) issue(g + 1);
           continue;
         }
+        if (clustered) {
+          add_partials(c * 32, va);
+          if (two) add_partials(c * 32 + 32, vb);
+        }
         if (fast) {
           const int row0 = tile_a * kTileA + quarter * 32;
           const int col0 = tile_b * p.bn + c * 32;
@@ -262,7 +307,7 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(ptx::smem_u32(tempty_bar + buf));
 
-      if (p.splits > 1) {
+      if (p.splits > 1 && !clustered) {
         // split-K: the last CTA to arrive for this tile sums all partial tiles.
         __threadfence();
         ptx::named_bar_sync(1, kEpiThreads);
@@ -299,6 +344,8 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncwarp();
   ptx::tc_fence_before_sync();
   __syncthreads();
+  // no CTA of a cluster leaves while a peer may still write its shared memory or barriers
+  if (clustered) ptx::cluster_sync_all();
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, static_cast<uint32_t>(p.tmem_cols));
@@ -402,19 +449,27 @@ namespace {
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-template <typename OutT, int MODE>
-cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp,
-                          const UmmaPlan& plan, cudaStream_t stream) {
+template <typename OutT, int MODE, bool CLUSTER>
+cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp,
+                           const UmmaPlan& plan, cudaStream_t stream) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = w8a8_umma_kernel<OutT, MODE>;
+  auto kern = w8a8_umma_kernel<OutT, MODE, CLUSTER>;
   if (dev < 64 && !attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  return launch_overlapped(kern, plan.grid, kThreads, plan.smem_bytes, stream, ta, tb, kp);
+  return launch_clustered(plan.cluster, true, kern, plan.grid, kThreads, plan.smem_bytes, stream, ta,
+                          tb, kp);
+}
+
+template <typename OutT, int MODE>
+cudaError_t launch_kernel(const CUtensorMap& ta, const CUtensorMap& tb, const KernelParams& kp,
+                          const UmmaPlan& plan, cudaStream_t stream) {
+  return plan.cluster > 1 ? launch_variant<OutT, MODE, true>(ta, tb, kp, plan, stream)
+                          : launch_variant<OutT, MODE, false>(ta, tb, kp, plan, stream);
 }
 
 }  // namespace
@@ -465,9 +520,35 @@ bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan) {
   if (splits > pl.k_blocks) splits = pl.k_blocks;
   pl.kb_per_split = (pl.k_blocks + splits - 1) / splits;
   pl.splits = (pl.k_blocks + pl.kb_per_split - 1) / pl.kb_per_split;
-  if (pl.splits > 1 && tiles * sizeof(unsigned int) > kCounterBytes) return false;
+  // Few tiles with a long K loop (decode batches of 64-512 tokens on the narrow projections):
+  // a cluster of 2 or 4 CTAs splits K and the leader adds the peers' partial tiles from its own
+  // shared memory — no trip through global memory, unlike the split above.
+  pl.cluster = 1;
+  pl.partial_bytes = 0;
+  if (op == B200Q_OP_W8A8 && !swap && pl.splits == 1) {
+    // worth it when the leader's K loop gets at least 8 blocks (about 1.7 us) shorter: the
+    // cluster launch, its two barriers and the reduction cost about a microsecond
+    int cl = 1;
+    for (int cand : {4, 2})
+      if (tiles * cand <= sms && pl.k_blocks / cand >= 3 &&
+          pl.k_blocks - (pl.k_blocks + cand - 1) / cand >= 8) {
+        cl = cand;
+        break;
+      }
+    cl = env_int("B200Q_DEBUG_CLUSTER", cl);
+    if (cl == 2 || cl == 4) {
+      const int per = (pl.k_blocks + cl - 1) / cl;
+      if (tiles * cl <= sms && per * (cl - 1) < pl.k_blocks) {
+        pl.cluster = cl;
+        pl.splits = cl;
+        pl.kb_per_split = per;
+        pl.partial_bytes = (cl - 1) * bn * kTileA * static_cast<int>(sizeof(int32_t));
+      }
+    }
+  }
+  if (pl.splits > 1 && pl.cluster == 1 && tiles * sizeof(unsigned int) > kCounterBytes) return false;
   const int stage_bytes = kTileA * kBlockK + bn * kBlockK;
-  constexpr int kFixedSmem = kStagingBytes + kScaleSmemBytes + kCtrlBytes;
+  const int kFixedSmem = pl.partial_bytes + kStagingBytes + kScaleSmemBytes + kCtrlBytes;
   int stages = (kMaxSmem - kFixedSmem) / stage_bytes;
   stages = std::min(stages, kMaxStages);
   stages = std::min(stages, std::max(2, pl.kb_per_split * 2));
@@ -478,7 +559,7 @@ bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan) {
   pl.tmem_cols = cols;
   const long long items = tiles * pl.splits;
   pl.grid = static_cast<int>(std::min<long long>(items, sms));
-  pl.ws_bytes = pl.splits > 1
+  pl.ws_bytes = (pl.splits > 1 && pl.cluster == 1)
                     ? kCounterBytes + static_cast<size_t>(tiles) * pl.splits * bn * kTileA * sizeof(int32_t)
                     : 0;
   *plan = pl;
@@ -496,8 +577,9 @@ int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
   if (!get_tensor_map(base_b, plan.rows_b, a.K, plan.bn, kBlockK, &tb)) return B200Q_ERR_LAUNCH;
   // Prefill orientation, 16-bit output, no split-K: outputs are transposed through shared
   // memory so that every store instruction writes complete 128-byte lines.
-  const bool fast_store = !plan.swap && a.acc_out == nullptr && plan.splits == 1 &&
-                          (a.N % 8) == 0 && (plan.bn % 64) == 0;
+  const bool fast_store = !plan.swap && a.acc_out == nullptr &&
+                          (plan.splits == 1 || plan.cluster > 1) && (a.N % 8) == 0 &&
+                          (plan.bn % 64) == 0;
 
   KernelParams kp{};
   kp.rows_a = plan.rows_a;
@@ -509,6 +591,8 @@ int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
   kp.splits = plan.splits;
   kp.kb_per_split = plan.kb_per_split;
   kp.stages = plan.stages;
+  kp.cluster = plan.cluster;
+  kp.partial_bytes = plan.partial_bytes;
   kp.tmem_cols = plan.tmem_cols;
   kp.swap = plan.swap;
   kp.n_channels = a.N;

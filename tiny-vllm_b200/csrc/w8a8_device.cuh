@@ -32,6 +32,8 @@ struct KernelParams {
   int tiles_a, tiles_b;
   int k_blocks, splits, kb_per_split;
   int stages;
+  int cluster;             // CTAs per cluster splitting K (1 = off); split index = cluster rank
+  int partial_bytes;       // shared memory the cluster leader receives partial tiles in
   int tmem_cols;
   int swap;
   int n_channels;          // leading dimension of the output
