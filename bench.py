@@ -57,25 +57,34 @@ def load_peaks():
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_sweep_seconds(tokens: int, repeats: int):
-    """Best-of-``repeats`` wall time of the CPU oracle's W8A8 path (per-token quantise, then
-    dequantise both operands and matmul) over the four projections for ``tokens`` tokens."""
+def cpu_problems(tokens: int):
+    """Seeded inputs of the four projections for ``tokens`` tokens (made outside any timing)."""
     from oracle import quant_linear_oracle as O
     problems = []
     for i, (_, K, N, _) in enumerate(PROJECTIONS):
         q, s = O.make_weight(N, K, seed=i)
         x = O.make_activation(tokens, K, seed=i)
         problems.append((x, q, s))
-    best = float("inf")
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        for x, q, s in problems:
-            xf = x.float()
-            a_s = (xf.abs().amax(dim=1) / 127.0).clamp_min(1e-8)
-            xq = torch.round(xf / a_s[:, None]).clamp(-127, 127).to(torch.int8)
-            O.w8a8_dequant_matmul(xq, a_s, q, s, None, torch.bfloat16)
-        best = min(best, time.perf_counter() - t0)
-    return best
+    return problems
+
+
+def cpu_sweep_once(problems) -> float:
+    """Wall time of one pass of the CPU oracle's W8A8 path (per-token quantise, then dequantise
+    both operands and matmul) over the four projections."""
+    from oracle import quant_linear_oracle as O
+    t0 = time.perf_counter()
+    for x, q, s in problems:
+        xf = x.float()
+        a_s = (xf.abs().amax(dim=1) / 127.0).clamp_min(1e-8)
+        xq = torch.round(xf / a_s[:, None]).clamp(-127, 127).to(torch.int8)
+        O.w8a8_dequant_matmul(xq, a_s, q, s, None, torch.bfloat16)
+    return time.perf_counter() - t0
+
+
+def cpu_sweep_seconds(tokens: int, repeats: int):
+    """Best-of-``repeats`` wall time of one pass for ``tokens`` tokens."""
+    problems = cpu_problems(tokens)
+    return min(cpu_sweep_once(problems) for _ in range(repeats))
 
 
 def use_all_host_threads() -> int:
@@ -112,13 +121,11 @@ def run_reference_arm(args):
     t_probe = cpu_sweep_seconds(256, 1)
     tokens = int(min(TOKENS, max(256, 1.5 / (t_probe / 256))))  # about 1.5 s per step at most
     tokens = max(256, tokens // 256 * 256)
+    problems = cpu_problems(tokens)          # inputs are made once, outside the timed steps
     for _ in range(max(0, min(args.warmup, 3))):
-        cpu_sweep_seconds(tokens, 1)
+        cpu_sweep_once(problems)
     steps = max(1, min(args.steps, 20))
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        cpu_sweep_seconds(tokens, 1)
-    dt = (time.perf_counter() - t0) / steps
+    dt = sum(cpu_sweep_once(problems) for _ in range(steps)) / steps
     value = total_ops(tokens) / dt / 1e12
     sample = (f"{tokens} of {TOKENS} tokens per step, {steps} timed steps, torch CPU bf16 "
               f"dequantize-then-matmul (oracle port of the reference's Python path)")
