@@ -554,6 +554,11 @@ def run_shape_sweep(args):
         a_s = torch.rand(M, device=dev)
         w_s = torch.rand(N, device=dev)
         y = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(nbuf)]
+        res = [torch.randn(M, K, dtype=torch.bfloat16, device=dev) for _ in range(nbuf)] \
+            if op == "add_rmsnorm_quant" else None
+        gu = [torch.randn(M, 2 * K, dtype=torch.bfloat16, device=dev) for _ in range(nbuf)] \
+            if op == "silu_mul_quant" else None
+        norm_w = torch.ones(K, dtype=torch.bfloat16, device=dev)
         side = torch.cuda.Stream(device=dev)
 
         def call(i, st):
@@ -566,9 +571,16 @@ def run_shape_sweep(args):
                 rc = L.b200q_w8a16_gemm(xb[j].data_ptr(), wq[j].data_ptr(), w_s.data_ptr(), None,
                                         y[j].data_ptr(), M, N, K, _lib.DTYPE_BF16, ws.data_ptr(),
                                         ws.numel(), st)
-            else:
+            elif op == "act_quant":
                 rc = L.b200q_act_quant_i8(xb[j].data_ptr(), K, _lib.DTYPE_BF16, xq[j].data_ptr(),
                                           a_s.data_ptr(), M, K, st)
+            elif op == "add_rmsnorm_quant":   # x + residual -> new residual (in place), codes
+                rc = L.b200q_add_rmsnorm_quant_i8(xb[j].data_ptr(), res[j].data_ptr(), norm_w.data_ptr(),
+                                                  1e-6, res[j].data_ptr(), None, xq[j].data_ptr(),
+                                                  a_s.data_ptr(), M, K, _lib.DTYPE_BF16, st)
+            else:                             # silu_mul_quant: [M, 2 K] -> codes [M, K]
+                rc = L.b200q_silu_mul_quant_i8(gu[j].data_ptr(), 2 * K, None, xq[j].data_ptr(),
+                                               a_s.data_ptr(), M, K, _lib.DTYPE_BF16, st)
             _lib.check(rc, op)
 
         for i in range(3):
@@ -590,7 +602,7 @@ def run_shape_sweep(args):
 
     results = []
     shapes = [(name, n, k) for name, k, n, _ in PROJECTIONS]
-    want_ops = args.sweep_op.split(",") if args.sweep_op else ["w8a8", "w8a16", "act_quant"]
+    want_ops = args.sweep_op.split(",") if args.sweep_op else ["w8a8", "w8a16", "act_quant", "fused_quant"]
     want_m = [int(m) for m in args.sweep_m.split(",")] if args.sweep_m else [1, 16, 128, 512, TOKENS]
     for op in ("w8a8", "w8a16"):
         if op not in want_ops:
@@ -615,6 +627,15 @@ def run_shape_sweep(args):
         results.append({"op": "act_quant", "proj": name, "M": TOKENS, "K": K, "us": round(us, 2),
                         "algorithmic_gbs": round(b / us / 1e3, 1),
                         "hbm_frac": round(b / us / 1e3 / peaks["hbm_gbs"], 3)})
+    if "fused_quant" in want_ops:
+        # quantisation fused into its producers: hidden-size rows (norm) and intermediate-size
+        # rows (activation) of Qwen3-0.6B at the prefill token count
+        for op, K, per_row in (("add_rmsnorm_quant", 1024, 7 * 1024 + 4), ("silu_mul_quant", 3072, 5 * 3072 + 4)):
+            us = time_op(op, TOKENS, 8, K, 50)
+            b = per_row * TOKENS
+            results.append({"op": op, "M": TOKENS, "K": K, "us": round(us, 2),
+                            "algorithmic_gbs": round(b / us / 1e3, 1),
+                            "hbm_frac": round(b / us / 1e3 / peaks["hbm_gbs"], 3)})
     print(json.dumps({"mode": "shape_sweep", "peaks": peaks, "device_status": L.b200q_device_status(),
                       "results": results}))
 
@@ -631,7 +652,7 @@ def main():
                          "replaying one CUDA graph per step")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="sum row-parallel outputs with NCCL instead of the peer-memory kernel")
-    ap.add_argument("--sweep-op", default="", help="shape_sweep: comma list of w8a8,w8a16,act_quant")
+    ap.add_argument("--sweep-op", default="", help="shape_sweep: comma list of w8a8,w8a16,act_quant,fused_quant")
     ap.add_argument("--sweep-m", default="", help="shape_sweep: comma list of token counts")
     ap.add_argument("--mode", default="headline", choices=["headline", "shape_sweep"],
                     help="shape_sweep prints per-shape kernel times (decode and prefill shapes)")

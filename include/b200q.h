@@ -86,6 +86,31 @@ int b200q_act_quant_i8(const void* x, int64_t ldx, int x_dtype, int8_t* xq, floa
                        int M, int K, void* stream);
 
 /*
+ * The same quantisation fused into the two operations that produce the inputs of the W8A8
+ * layers in the reference's model (nanovllm/models/qwen3.py:119-121,160-166), so that the
+ * 16-bit activation is never written to and re-read from memory (no counterpart in the
+ * reference, which runs the producer and the quantiser as separate steps).
+ *
+ * b200q_add_rmsnorm_quant_i8 — RMSNorm.forward of nanovllm/layers/layernorm.py:16-50:
+ *   s = float(x) + float(residual_in)   (residual_in may be NULL: s = float(x))
+ *   residual_out = T(s)                 (skipped when residual_out is NULL; may alias residual_in, not x)
+ *   y = T(T(s * rsqrt(mean_k(s^2) + eps)) * weight)
+ *   (xq, a_scales) = per-token quantisation of y, bit-identical to b200q_act_quant_i8(y)
+ * x, residual_*, y: dense [M, K] of `dtype`; weight: [K] of `dtype`; y is written only when
+ * non-NULL.  K % 16 == 0, K <= 16384.
+ *
+ * b200q_silu_mul_quant_i8 — SiluAndMul.forward of nanovllm/layers/activation.py:11-14:
+ *   y = T(silu(float(gate)) * float(up)) with gate = gate_up[:, 0:I], up = gate_up[:, I:2I]
+ *   (row pitch ld elements, ld >= 2 I, ld % 8 == 0), then the same quantisation of y.
+ * I % 16 == 0, I <= 16384.
+ */
+int b200q_add_rmsnorm_quant_i8(const void* x, const void* residual_in, const void* weight, float eps,
+                               void* residual_out, void* y, int8_t* xq, float* a_scales, int M,
+                               int K, int dtype, void* stream);
+int b200q_silu_mul_quant_i8(const void* gate_up, int64_t ld, void* y, int8_t* xq, float* a_scales,
+                            int M, int I, int dtype, void* stream);
+
+/*
  * W8A8 linear: acc[m,n] = sum_k xq[m,k] * qweight[n,k] (exact int32), then
  *   y[m,n] = out_dtype( (float(acc) * a_scales[m]) * w_scales[n] + bias[n] )
  * bias may be NULL; when given it has dtype out_dtype and length N.

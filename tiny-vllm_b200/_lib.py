@@ -75,6 +75,11 @@ SIGNATURES = {
                                                    _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
                                                    _c.c_int, _c.c_int, _c.c_void_p, _c.c_size_t,
                                                    _c.c_void_p, _c.c_int, _c.c_int, _c.c_void_p]),
+    "b200q_add_rmsnorm_quant_i8": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_float,
+                                              _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                              _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),
+    "b200q_silu_mul_quant_i8": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p,
+                                           _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_void_p]),
     "b200q_tp_allreduce_multimem": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
                                                _c.c_size_t, _c.c_int, _c.c_void_p]),
     "b200q_tp_allreduce_pull": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,

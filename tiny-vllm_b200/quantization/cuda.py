@@ -100,6 +100,61 @@ def quantize_activation_int8(x_2d: torch.Tensor) -> tuple[torch.Tensor, torch.Te
     return x_q, a_scales
 
 
+def add_rmsnorm_quantize_int8(x: torch.Tensor, weight: torch.Tensor, eps: float,
+                              residual: torch.Tensor | None = None, return_normed: bool = False):
+    """RMSNorm (optionally with the residual add in front) and the per-token int8 quantisation
+    of its output in one kernel: what ``RMSNorm.forward`` (``nanovllm/layers/layernorm.py:16-50``)
+    followed by ``quantize_int8_per_row_dynamic`` computes, without the 16-bit round trip.
+
+    ``x``: ``[..., K]`` fp16/bf16; ``weight``: ``[K]`` same dtype; ``residual``: like ``x`` or
+    ``None``.  Returns ``(x_q [M, K] int8, a_scales [M] fp32, new_residual or None, normed or
+    None)`` with ``M`` the flattened token count; ``new_residual`` has ``x``'s shape."""
+    _require_cuda(x, weight)
+    if x.dtype not in _DTYPE_IDS or weight.dtype != x.dtype or weight.dim() != 1 \
+            or weight.numel() != x.shape[-1]:
+        raise RuntimeError("add_rmsnorm_quantize_int8 expects fp16/bf16 x and a weight of its width and dtype")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype or not residual.is_cuda):
+        raise RuntimeError("residual must match x in shape, dtype and device")
+    K = x.shape[-1]
+    x2 = x.contiguous().view(-1, K)
+    M = x2.shape[0]
+    r2 = None if residual is None else residual.contiguous().view(-1, K)
+    x_q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    a_s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    new_res = torch.empty_like(x2) if residual is not None else None
+    normed = torch.empty_like(x2) if return_normed else None
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().b200q_add_rmsnorm_quant_i8(
+            x2.data_ptr(), None if r2 is None else r2.data_ptr(), weight.contiguous().data_ptr(),
+            float(eps), None if new_res is None else new_res.data_ptr(),
+            None if normed is None else normed.data_ptr(), x_q.data_ptr(), a_s.data_ptr(), M, K,
+            _DTYPE_IDS[x.dtype], _stream_ptr(x.device))
+    _lib.check(rc, "b200q_add_rmsnorm_quant_i8", f"M={M} K={K}")
+    return (x_q, a_s, None if new_res is None else new_res.view(x.shape),
+            None if normed is None else normed.view(x.shape))
+
+
+def silu_mul_quantize_int8(gate_up: torch.Tensor, return_act: bool = False):
+    """``SiluAndMul.forward`` (``nanovllm/layers/activation.py:11-14``) and the per-token int8
+    quantisation of its output in one kernel.  ``gate_up``: ``[..., 2 I]`` fp16/bf16.  Returns
+    ``(x_q [M, I] int8, a_scales [M] fp32, act [..., I] or None)``."""
+    _require_cuda(gate_up)
+    if gate_up.dtype not in _DTYPE_IDS or gate_up.shape[-1] % 2 != 0:
+        raise RuntimeError("silu_mul_quantize_int8 expects an fp16/bf16 tensor with an even last dimension")
+    two_i = gate_up.shape[-1]
+    g2 = gate_up.contiguous().view(-1, two_i)
+    M, inter = g2.shape[0], two_i // 2
+    x_q = torch.empty((M, inter), dtype=torch.int8, device=gate_up.device)
+    a_s = torch.empty((M,), dtype=torch.float32, device=gate_up.device)
+    act = torch.empty((M, inter), dtype=gate_up.dtype, device=gate_up.device) if return_act else None
+    with torch.cuda.device(gate_up.device):
+        rc = _lib.lib().b200q_silu_mul_quant_i8(g2.data_ptr(), two_i, None if act is None else act.data_ptr(),
+                                                x_q.data_ptr(), a_s.data_ptr(), M, inter,
+                                                _DTYPE_IDS[gate_up.dtype], _stream_ptr(gate_up.device))
+    _lib.check(rc, "b200q_silu_mul_quant_i8", f"M={M} I={inter}")
+    return x_q, a_s, None if act is None else act.view(*gate_up.shape[:-1], inter)
+
+
 def _check_w8a16(x, qweight, scales, bias) -> None:
     _require_cuda(x, qweight, scales)
     if x.dtype not in _DTYPE_IDS or qweight.dtype != torch.int8 or scales.dtype != torch.float32:
