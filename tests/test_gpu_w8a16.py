@@ -5,7 +5,8 @@ import torch
 
 from oracle import quant_linear_oracle as O
 from gpu_util import bits, device_status_ok, forced_path
-from tiny_vllm_b200.quantization.cuda import apply_int8_weight_only_linear
+from tiny_vllm_b200 import _lib
+from tiny_vllm_b200.quantization.cuda import apply_int8_weight_only_linear, select_path
 
 pytestmark = pytest.mark.gpu
 
@@ -74,6 +75,30 @@ def test_prefill_kernel_ragged_edges(M, N, K, dtype, bias):
     y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda())
     m = O.tensor_metrics(O.w8a16_native_reference(x, q, s, b), y)
     assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
+    assert device_status_ok()
+
+
+@pytest.mark.parametrize("M,N,K,dtype,bias", [(2500, 2056, 272, torch.bfloat16, True),
+                                              (2305, 2304, 1024, torch.float16, False),
+                                              (5000, 1024, 2048, torch.bfloat16, False)])
+def test_tensor_memory_weights_kernel(M, N, K, dtype, bias, monkeypatch):
+    # the prefill variant that keeps the expanded weights in tensor memory (default for K >= 2048),
+    # forced here for ragged M / N and a K tail as well
+    monkeypatch.setenv("B200Q_DEBUG_TS_MIN_K", "16")
+    assert select_path(_lib.OP_W8A16, M, N, K) == "umma_f16_tmem_weights_channels256"
+    q, s = O.make_weight(N, K, seed=N)
+    x = O.make_activation(M, K, seed=M, dtype=dtype, outliers=False)
+    b = (torch.randn(N, generator=torch.Generator().manual_seed(1)) * 0.1).to(dtype) if bias else None
+    y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda())
+    m = O.tensor_metrics(O.w8a16_native_reference(x, q, s, b), y)
+    assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
+    # every int8 code expands exactly: identity activations select weight columns
+    Kc, Mc, Nc = 256, 2560, 2048
+    qc = torch.stack([torch.roll(torch.arange(-128, 128, dtype=torch.int16).to(torch.int8), i)
+                      for i in range(Nc)])
+    xc = torch.eye(Kc, dtype=dtype).repeat(Mc // Kc, 1)
+    yc = apply_int8_weight_only_linear(xc.cuda(), qc.cuda(), torch.ones(Nc).cuda())
+    assert torch.equal(yc.float().cpu(), qc.float().T.repeat(Mc // Kc, 1))
     assert device_status_ok()
 
 

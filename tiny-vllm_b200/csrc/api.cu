@@ -384,6 +384,7 @@ int b200q_w8a16_gemm(const void* x, const int8_t* qweight, const float* scales, 
     }
     return B200Q_OK;
   }
+  if (path == B200Q_PATH_UMMA && umma16_ts_applicable(M, N, K)) return launch_w8a16_umma_ts(a);
   if (path == B200Q_PATH_UMMA || path == B200Q_PATH_UMMA_SWAP) {
     UmmaPlan plan;
     if (!umma16_make_plan(M, N, K, path == B200Q_PATH_UMMA_SWAP, &plan))
@@ -394,6 +395,9 @@ int b200q_w8a16_gemm(const void* x, const int8_t* qweight, const float* scales, 
 }
 
 size_t b200q_workspace_bytes(int op, int M, int N, int K) {
+  if (op == B200Q_OP_W8A16 && check_dims(M, N, K) == B200Q_OK &&
+      resolve_path(op, M, N, K) == B200Q_PATH_UMMA && umma16_ts_applicable(M, N, K))
+    return 0;
   if (op != B200Q_OP_W8A8 && op != B200Q_OP_W8A16) return 0;
   if (check_dims(M, N, K) != B200Q_OK) return 0;
   const int path = resolve_path(op, M, N, K);
@@ -418,6 +422,7 @@ const char* b200q_select_path(int op, int M, int N, int K) {
       return a16 ? "mma_stream_w8a16_splitk" : "mma_stream_s8_splitk";
     case B200Q_PATH_UMMA:
       if (!a16 && umma_pair_applicable(M, N, K, false)) return "umma_i8_pair_tokens256";
+      if (a16 && umma16_ts_applicable(M, N, K)) return "umma_f16_tmem_weights_channels256";
       return a16 ? "umma_f16_expand_tokens128" : "umma_i8_tokens128";
     case B200Q_PATH_UMMA_SWAP:
       return a16 ? "umma_f16_expand_channels128_splitk" : "umma_i8_channels128_splitk";

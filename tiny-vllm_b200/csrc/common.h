@@ -100,6 +100,10 @@ int launch_tp_reduce_gather(const void* stage, void* const* peer_y,
 bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan);
 int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan);
 
+// gemm_umma_w8a16_ts.cu: prefill variant with the expanded weights in tensor memory
+bool umma16_ts_applicable(int M, int N, int K);
+int launch_w8a16_umma_ts(const GemmArgs& a);
+
 // Launches `kernel` so that it may overlap its start-up (barrier set-up, TMEM allocation,
 // descriptor prefetch, launch latency) with the tail of the previous kernel in the stream
 // (programmatic dependent launch).  Only for kernels that call ptx::grid_dependency_wait()
