@@ -13,13 +13,14 @@
 // in use, so the accumulators are single-buffered: the epilogue of a tile does not overlap
 // the main loop of the next.
 //
-// Warp roles (448 threads, 1 CTA per SM, persistent):
+// Warp roles (704 threads, 1 CTA per SM, persistent):
 //   warp 0      TMA producer: token tile (128 x 128 B, 128-byte swizzle) + raw int8 tile
 //               (256 x 64 B, 64-byte swizzle) per K block of 64 elements
 //   warp 1      UMMA issuer (one thread): 2 x 4 tcgen05.mma (A from tensor memory) per block
 //   warps 2-5   epilogue: tcgen05.ld -> acc * s[n] + b[n] -> 16 bit -> y[token][channel]
-//   warps 6-13  converters: warp w owns TMEM lanes 32 (w % 4) .. + 31 of channel tile
-//               (w - 6) / 4: one raw row per thread -> 32 packed words -> tcgen05.st
+//   warps 6-21  converters, two groups of eight taking K blocks in turn: warp w owns TMEM
+//               lanes 32 (w % 4) .. + 31 of one channel tile: one raw row per thread -> 32
+//               packed words -> tcgen05.st
 // Every mbarrier wait is bounded.  Arithmetic as in the shared-memory kernel: fp32 sums of
 // x * float(q), then acc * s[n] + b[n]
 // (nanovllm/quantization/csrc/int8_weight_only_gemm.cu:258-292, 397-412).
@@ -49,6 +50,8 @@ constexpr int kTsCtrlBytes = 512;
 constexpr int kTsStageOutBytes = 32 * kTileA * 2;
 constexpr int kTsSmem = kTsStages * kTsStageBytes + 2 * kTsStageOutBytes + kTsCtrlBytes;
 constexpr int kTsTmemCols = 512;
+constexpr int kTsConvGroups = 2;   // converter groups taking K blocks in turn
+constexpr int kTsThreads = 64 + kEpiThreads + kTsConvGroups * kConvThreads;  // 704
 constexpr int kTsAcol0 = 256;      // first column of the A ring
 constexpr int kTsAStageCols = 64;  // two tiles x 32 columns
 
@@ -64,7 +67,7 @@ struct TsParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(kTsThreads, 1)
 w8a16_umma_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
                      const __grid_constant__ CUtensorMap tmap_w, const TsParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -187,17 +190,22 @@ w8a16_umma_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
   } else if (warp >= 2 + kEpiWarps) {
     // ---------------------------------------------------------- converters
-    const int cw = warp - (2 + kEpiWarps);       // 0..7
-    const int tile = cw >> 2;                    // channel tile of this warp
+    // One K block is a dependent chain per thread (wait, 4 loads, expansion, tcgen05.st, wait,
+    // arrive); two groups of eight warps take the blocks in turn so that two chains overlap.
+    const int cw = warp - (2 + kEpiWarps);       // 0..15
+    const int group = cw >> 3;                   // blocks group, group + 2, ...
+    const int tile = (cw & 7) >> 2;              // channel tile of this warp
     const int quarter = warp & 3;                // TMEM lane quarter this warp may access
     const int r = tile * kTileA + quarter * 32 + lane;  // raw row (channel) of this thread
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kTsAcol0 +
                                static_cast<uint32_t>(tile * 32);
-    int stage = 0, as = 0;
-    uint32_t phase = 0, aphase = 0;
+    uint32_t blk = 0;  // K blocks seen so far, over all items
     bool ok = true;
     for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int kb = 0; kb < p.k_blocks; ++kb, ++blk) {
+        if (static_cast<int>(blk & 1u) != group) continue;
+        const uint32_t stage = blk % kTsStages, phase = (blk / kTsStages) & 1u;
+        const uint32_t as = blk % kTsAStages, aphase = (blk / kTsAStages) & 1u;
         if (!ptx::mbar_wait(ptx::smem_u32(full_bar + stage), phase, abort_flag) ||
             !ptx::mbar_wait(ptx::smem_u32(aempty_bar + as), aphase ^ 1u, abort_flag)) {
           ok = false;
@@ -222,19 +230,11 @@ w8a16_umma_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
           v[8 * c + 6] = e3.x;
           v[8 * c + 7] = e3.y;
         }
-        ptx::tmem_st_32x32b_x32(lane_base + static_cast<uint32_t>(as * kTsAStageCols), v);
+        ptx::tmem_st_32x32b_x32(lane_base + as * kTsAStageCols, v);
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(afull_bar + as));
-        if (++stage == kTsStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
-        if (++as == kTsAStages) {
-          as = 0;
-          aphase ^= 1u;
-        }
       }
     }
   } else {
@@ -316,15 +316,15 @@ cudaError_t launch_ts(const CUtensorMap& tx, const CUtensorMap& tw, const TsPara
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  return launch_overlapped(kern, grid, kThreads, kTsSmem, stream, tx, tw, tp);
+  return launch_overlapped(kern, grid, kTsThreads, kTsSmem, stream, tx, tw, tp);
 }
 
 }  // namespace
 
 // Prefill-sized problems with enough 256 x 128 tiles to fill the GPU and a long K loop: the
 // epilogue of a tile is not overlapped here (all of tensor memory is in use), so the kernel
-// wins where the main loop dominates (M = 8192: 2048 -> 1024 47.0 vs 49.9 us, 3072 -> 1024
-// 65.7 vs 71.3 us) and loses at K = 1024 (88.9 vs 87.1 us, 136.6 vs 131.5 us).
+// wins where the main loop dominates (M = 8192: 2048 -> 1024 44.6 vs 49.9 us, 3072 -> 1024
+// 62.3 vs 71.3 us) and not at K = 1024 (88.0 vs 87.1 us, 133.7 vs 131.5 us).
 bool umma16_ts_applicable(int M, int N, int K) {
   if (env_int("B200Q_DEBUG_NO_TS", 0) != 0) return false;
   if (K < env_int("B200Q_DEBUG_TS_MIN_K", 2048)) return false;
