@@ -13,12 +13,13 @@
 // in use, so the accumulators are single-buffered: the epilogue of a tile does not overlap
 // the main loop of the next.
 //
-// Warp roles (704 threads, 1 CTA per SM, persistent):
+// Warp roles (832 threads, 1 CTA per SM, persistent):
 //   warp 0      TMA producer: token tile (128 x 128 B, 128-byte swizzle) + raw int8 tile
 //               (256 x 64 B, 64-byte swizzle) per K block of 64 elements
 //   warp 1      UMMA issuer (one thread): 2 x 4 tcgen05.mma (A from tensor memory) per block
-//   warps 2-5   epilogue: tcgen05.ld -> acc * s[n] + b[n] -> 16 bit -> y[token][channel]
-//   warps 6-21  converters, two groups of eight taking K blocks in turn: warp w owns TMEM
+//   warps 2-9   epilogue, four warps per channel tile: tcgen05.ld -> acc * s[n] + b[n] ->
+//               16 bit -> y[token][channel]
+//   warps 10-25 converters, two groups of eight taking K blocks in turn: warp w owns TMEM
 //               lanes 32 (w % 4) .. + 31 of one channel tile: one raw row per thread -> 32
 //               packed words -> tcgen05.st
 // Every mbarrier wait is bounded.  Arithmetic as in the shared-memory kernel: fp32 sums of
@@ -46,12 +47,14 @@ constexpr int kTsStageBytes = kTsTokBytes + kTsRawBytes;
 constexpr int kTsStages = 6;
 constexpr int kTsAStages = 4;
 constexpr int kTsCtrlBytes = 512;
-// epilogue staging: two buffers of 32 tokens x 128 channels, 16 bit
+// epilogue staging: per channel tile two buffers of 32 tokens x 128 channels, 16 bit
 constexpr int kTsStageOutBytes = 32 * kTileA * 2;
-constexpr int kTsSmem = kTsStages * kTsStageBytes + 2 * kTsStageOutBytes + kTsCtrlBytes;
+constexpr int kTsEpiWarps = 8;     // four per channel tile (one per TMEM lane quarter)
+constexpr int kTsEpiThreads = kTsEpiWarps * 32;
+constexpr int kTsSmem = kTsStages * kTsStageBytes + 4 * kTsStageOutBytes + kTsCtrlBytes;
 constexpr int kTsTmemCols = 512;
 constexpr int kTsConvGroups = 2;   // converter groups taking K blocks in turn
-constexpr int kTsThreads = 64 + kEpiThreads + kTsConvGroups * kConvThreads;  // 704
+constexpr int kTsThreads = 64 + kTsEpiThreads + kTsConvGroups * kConvThreads;  // 832
 constexpr int kTsAcol0 = 256;      // first column of the A ring
 constexpr int kTsAStageCols = 64;  // two tiles x 32 columns
 
@@ -72,7 +75,7 @@ w8a16_umma_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
                      const __grid_constant__ CUtensorMap tmap_w, const TsParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* out_stage = smem + kTsStages * kTsStageBytes;
-  uint8_t* ctrl = out_stage + 2 * kTsStageOutBytes;
+  uint8_t* ctrl = out_stage + 4 * kTsStageOutBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);   // [stages] TMA bytes landed
   uint64_t* empty_bar = full_bar + kTsStages;               // [stages] MMAs that read it are done
   uint64_t* afull_bar = empty_bar + kTsStages;              // [a stages] expansion written
@@ -100,7 +103,7 @@ w8a16_umma_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
       ptx::mbar_init(ptx::smem_u32(aempty_bar + s), 1);
     }
     ptx::mbar_init(ptx::smem_u32(tfull_bar), 1);
-    ptx::mbar_init(ptx::smem_u32(tempty_bar), kEpiThreads);
+    ptx::mbar_init(ptx::smem_u32(tempty_bar), kTsEpiThreads);
     *abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::tma_prefetch_desc(&tmap_x);
@@ -188,11 +191,11 @@ w8a16_umma_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (ok) ptx::umma_commit(ptx::smem_u32(tfull_bar));
       }
     }
-  } else if (warp >= 2 + kEpiWarps) {
+  } else if (warp >= 2 + kTsEpiWarps) {
     // ---------------------------------------------------------- converters
     // One K block is a dependent chain per thread (wait, 4 loads, expansion, tcgen05.st, wait,
     // arrive); two groups of eight warps take the blocks in turn so that two chains overlap.
-    const int cw = warp - (2 + kEpiWarps);       // 0..15
+    const int cw = warp - (2 + kTsEpiWarps);     // 0..15
     const int group = cw >> 3;                   // blocks group, group + 2, ...
     const int tile = (cw & 7) >> 2;              // channel tile of this warp
     const int quarter = warp & 3;                // TMEM lane quarter this warp may access
@@ -240,50 +243,50 @@ w8a16_umma_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else {
     // ------------------------------------------------------------ epilogue
     // A thread holds one channel (its TMEM lane) and 32 tokens per load, but y is token-major:
-    // the four warps put their 32 x 32 blocks side by side in shared memory as
-    // [token][128 channels] and then write whole 256-byte token rows, 16 bytes per lane.
+    // the four warps of a channel tile put their 32 x 32 blocks side by side in shared memory
+    // as [token][128 channels] and then write whole 256-byte token rows, 16 bytes per lane.
+    // Warps 2-5 drain channel tile 0, warps 6-9 channel tile 1, at the same time.
     const int quarter = warp & 3;
-    const int epi_warp = warp - 2;
+    const int t = (warp - 2) >> 2;                // channel tile of this warp
+    const int sub = (warp - 2) & 3;               // warp inside its group of four
     const T* bias = reinterpret_cast<const T*>(p.bias);
     T* out = reinterpret_cast<T*>(p.out);
+    uint8_t* my_stage = out_stage + t * 2 * kTsStageOutBytes;
     int it = 0, round = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
       const int tile_ch = item % p.tiles_ch;
       const int tile_tok = item / p.tiles_ch;
       if (!ptx::mbar_wait(ptx::smem_u32(tfull_bar), static_cast<uint32_t>(it) & 1u, abort_flag)) break;
       ptx::tc_fence_after_sync();
+      const int ch0 = tile_ch * kTsChannels + t * kTileA;       // first channel of this A tile
+      const int ch = ch0 + quarter * 32 + lane;
+      const bool ch_ok = ch < p.N;
+      const float s = ch_ok ? __ldg(p.w_scales + ch) : 0.f;
+      const float b = (ch_ok && bias != nullptr) ? to_float<T>(bias[ch]) : 0.f;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(t * kTsTokens);
 #pragma unroll 1
-      for (int t = 0; t < 2; ++t) {
-        const int ch0 = tile_ch * kTsChannels + t * kTileA;       // first channel of this A tile
-        const int ch = ch0 + quarter * 32 + lane;
-        const bool ch_ok = ch < p.N;
-        const float s = ch_ok ? __ldg(p.w_scales + ch) : 0.f;
-        const float b = (ch_ok && bias != nullptr) ? to_float<T>(bias[ch]) : 0.f;
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                               static_cast<uint32_t>(t * kTsTokens);
-#pragma unroll 1
-        for (int c = 0; c < kTsTokens / 32; ++c, ++round) {
-          uint32_t v[32];
-          ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
-          ptx::tmem_ld_wait();
-          if (p.debug_flags & 1) continue;
-          T* buf = reinterpret_cast<T*>(out_stage + (round & 1) * kTsStageOutBytes);
+      for (int c = 0; c < kTsTokens / 32; ++c, ++round) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
+        ptx::tmem_ld_wait();
+        if (p.debug_flags & 1) continue;
+        T* buf = reinterpret_cast<T*>(my_stage + (round & 1) * kTsStageOutBytes);
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            buf[j * kTileA + quarter * 32 + lane] = from_float<T>(scale_acc(__uint_as_float(v[j]), s, b));
-          // all four blocks are in place; passing this barrier also means that every warp has
-          // finished reading the other buffer (it did so before arriving here)
-          ptx::named_bar_sync(2, kEpiThreads);
-          const int tok0 = tile_tok * kTsTokens + c * 32;
+        for (int j = 0; j < 32; ++j)
+          buf[j * kTileA + quarter * 32 + lane] = from_float<T>(scale_acc(__uint_as_float(v[j]), s, b));
+        // all four blocks are in place; passing this barrier also means that every warp of the
+        // group has finished reading the other buffer (it did so before arriving here)
+        ptx::named_bar_sync(2 + t, kEpiThreads);
+        const int tok0 = tile_tok * kTsTokens + c * 32;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int j = epi_warp * 8 + i * 2 + (lane >> 4);   // token row inside the chunk
-            const int col = (lane & 15) * 8;                     // first of 8 channels
-            const int tok = tok0 + j;
-            if (tok < p.M && ch0 + col < p.N)                     // N % 8 == 0: all in or all out
-              *reinterpret_cast<uint4*>(out + static_cast<size_t>(tok) * p.N + ch0 + col) =
-                  *reinterpret_cast<const uint4*>(buf + j * kTileA + col);
-          }
+        for (int i = 0; i < 4; ++i) {
+          const int j = sub * 8 + i * 2 + (lane >> 4);       // token row inside the chunk
+          const int col = (lane & 15) * 8;                   // first of 8 channels
+          const int tok = tok0 + j;
+          if (tok < p.M && ch0 + col < p.N)                   // N % 8 == 0: all in or all out
+            *reinterpret_cast<uint4*>(out + static_cast<size_t>(tok) * p.N + ch0 + col) =
+                *reinterpret_cast<const uint4*>(buf + j * kTileA + col);
         }
       }
       ptx::tc_fence_before_sync();
@@ -321,13 +324,14 @@ cudaError_t launch_ts(const CUtensorMap& tx, const CUtensorMap& tw, const TsPara
 
 }  // namespace
 
-// Prefill-sized problems with enough 256 x 128 tiles to fill the GPU and a long K loop: the
-// epilogue of a tile is not overlapped here (all of tensor memory is in use), so the kernel
-// wins where the main loop dominates (M = 8192: 2048 -> 1024 44.6 vs 49.9 us, 3072 -> 1024
-// 62.3 vs 71.3 us) and not at K = 1024 (88.0 vs 87.1 us, 133.7 vs 131.5 us).
+// Prefill-sized problems with enough 256 x 128 tiles to fill the GPU and at least 16 K blocks:
+// the epilogue of a tile is not overlapped here (all of tensor memory is in use), so very short
+// K loops stay on the shared-memory kernel.  M = 8192, this kernel vs that one: 1024 -> 4096
+// 84.3 vs 87.1 us, 2048 -> 1024 44.8 vs 49.9 us, 1024 -> 6144 128.4 vs 131.5 us, 3072 -> 1024
+// 61.6 vs 71.3 us.
 bool umma16_ts_applicable(int M, int N, int K) {
   if (env_int("B200Q_DEBUG_NO_TS", 0) != 0) return false;
-  if (K < env_int("B200Q_DEBUG_TS_MIN_K", 2048)) return false;
+  if (K < env_int("B200Q_DEBUG_TS_MIN_K", 1024)) return false;
   if ((K % 16) != 0 || (N % 8) != 0) return false;   // 16-byte output pieces
   const long long tiles = static_cast<long long>((N + kTsChannels - 1) / kTsChannels) *
                           ((M + kTsTokens - 1) / kTsTokens);
