@@ -102,6 +102,19 @@ def test_tensor_memory_weights_kernel(M, N, K, dtype, bias, monkeypatch):
     assert device_status_ok()
 
 
+def test_prefill_with_odd_channel_count_stays_on_the_shared_memory_kernel():
+    # N % 8 != 0: no 16-byte output pieces, so neither the tensor-memory kernel nor the
+    # full-line store path applies; element-wise stores of the shared-memory kernel
+    M, N, K = 2600, 2052 + 2, 1040
+    assert select_path(_lib.OP_W8A16, M, N, K) == "umma_f16_expand_tokens128"
+    q, s = O.make_weight(N, K, seed=N)
+    x = O.make_activation(M, K, seed=M, outliers=False)
+    y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda())
+    m = O.tensor_metrics(O.w8a16_native_reference(x, q, s), y)
+    assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
+    assert device_status_ok()
+
+
 def test_prefill_kernel_expands_every_code_exactly():
     K, M, N = 256, 2560, 2048
     q = torch.stack([torch.roll(torch.arange(-128, 128, dtype=torch.int16).to(torch.int8), i)
