@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define B200Q_VERSION 1
+#define B200Q_VERSION 2
 
 /* ---- error codes ------------------------------------------------------- */
 enum {
@@ -181,11 +181,53 @@ int b200q_version(void);
  * Test hook: force a kernel family (B200Q_PATH_*) for the GEMM entry points, or
  * B200Q_PATH_AUTO to restore the built-in choice.  A family that cannot run the
  * given problem makes the call return B200Q_ERR_UNSUPPORTED_SHAPE.  Returns the
- * previous setting.  The reference exposes the same kind of switch through the
+ * previous setting.  Like every debug knob it applies to the CALLING THREAD only.
+ * The reference exposes the same kind of switch through the
  * NANOVLLM_INT8_BACKEND / NANOVLLM_W8A8_BACKEND variables
  * (nanovllm/quantization/cuda.py:46-53).
  */
 int b200q_debug_force_path(int path);
+
+/*
+ * Test and tuning knobs.  A knob changes which kernel variant runs, how a problem is tiled,
+ * or (B200Q_KNOB_FLAGS) switches parts of a kernel off so that their cost can be measured —
+ * the last kind makes results WRONG on purpose.  All knobs are unset when the library is
+ * loaded, nothing is read from the environment, and a setting is private to the thread
+ * that made it: a serving process that never calls b200q_debug_set() cannot be affected.
+ * b200q_debug_set returns 0, or -1 for an unknown knob; b200q_debug_reset unsets all knobs
+ * of the calling thread.  (The reference's counterparts are environment variables read on
+ * every forward: nanovllm/quantization/cuda.py:46-53,249.)
+ */
+enum {
+  B200Q_KNOB_FORCE_PATH = 0,       /* B200Q_PATH_* (same as b200q_debug_force_path) */
+  B200Q_KNOB_FLAGS = 1,            /* tcgen05 kernels: 1 skip epilogue arithmetic, 2 skip MMAs, 4 skip output stores */
+  B200Q_KNOB_BN = 2,               /* single-CTA kernels: UMMA N */
+  B200Q_KNOB_SPLITS = 3,           /* single-CTA kernels: split-K factor */
+  B200Q_KNOB_CLUSTER = 4,          /* single-CTA kernels: cluster split-K size */
+  B200Q_KNOB_NO_PAIR = 5,          /* 1: never take the CTA-pair kernels */
+  B200Q_KNOB_NO_TS = 6,            /* 1: never take the W8A16 kernel with weights in tensor memory */
+  B200Q_KNOB_TS_MIN_K = 7,         /* smallest K for that kernel */
+  B200Q_KNOB_SIMT_MAX_M = 8,       /* largest M that takes the SIMT cross-check kernels */
+  B200Q_KNOB_TILED_ONLY = 9,       /* fused prefill route: 1 = GEMM kernel only, 2 = sum-and-gather only */
+  B200Q_KNOB_PAIR_EPILOGUE = 10,   /* CTA-pair kernels: 0 st.global via shared memory, 1 TMA store (default) */
+  B200Q_KNOB_W8A16_PAIR_MIN_M = 11,/* smallest M for the expand-once W8A16 route */
+  B200Q_KNOB_NO_PDL = 12,          /* 1: plain stream order instead of programmatic dependent launch */
+  B200Q_KNOB_WAIT_CYCLES = 13,     /* limit of one wait on a peer GPU, in SM cycles (default about 2e9) */
+  B200Q_KNOB_PAIR_MIN_TILES = 14,  /* CTA-pair kernels: fewest 256 x 256 tiles a problem must have */
+  B200Q_KNOB_COUNT = 16
+};
+int b200q_debug_set(int knob, int value);
+void b200q_debug_reset(void);
+
+/*
+ * Reads and clears the device status word like b200q_device_status() (synchronous: call it
+ * after the stream has been synchronised) and turns it into a return code: B200Q_OK when no
+ * bounded wait gave up since the last read, else B200Q_ERR_DEVICE_TIMEOUT with the word in
+ * *status_word (may be NULL).  The reference has no counterpart: its kernels cannot time out,
+ * and a failing extension call is turned into a silent fallback
+ * (nanovllm/quantization/cuda.py:347-356,493-503); here the failure is reported.
+ */
+int b200q_check_status(int* status_word);
 
 /* Test hook: number of kernels this library has launched in this process. */
 uint64_t b200q_launch_count(void);

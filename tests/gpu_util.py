@@ -21,6 +21,23 @@ def forced_path(name):
         L.b200q_debug_force_path(prev)
 
 
+@contextlib.contextmanager
+def knobs(**settings):
+    """Runs the body with debug knobs set for this thread, e.g. ``knobs(CLUSTER=1)``
+    (names are the ``KNOB_*`` constants of ``_lib`` without the prefix); all knobs are unset
+    again afterwards, a forced kernel family included."""
+    L = _lib.lib()
+    path = L.b200q_debug_force_path(_lib.PATH_AUTO)
+    L.b200q_debug_force_path(path)
+    for name, value in settings.items():
+        assert L.b200q_debug_set(getattr(_lib, "KNOB_" + name), int(value)) == 0
+    try:
+        yield
+    finally:
+        L.b200q_debug_reset()
+        L.b200q_debug_force_path(path)
+
+
 def device_status_ok():
     torch.cuda.synchronize()
     return _lib.lib().b200q_device_status() == 0

@@ -34,7 +34,7 @@ def test_every_declared_symbol_is_exported(L):
 
 
 def test_version_and_strerror(L):
-    assert L.b200q_version() == 1
+    assert L.b200q_version() == _lib.ABI_VERSION
     assert L.b200q_strerror(0) == b"ok"
     for code in range(1, 10):
         assert len(L.b200q_strerror(code)) > 3

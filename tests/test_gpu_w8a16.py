@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import quant_linear_oracle as O
-from gpu_util import bits, device_status_ok, forced_path
+from gpu_util import bits, device_status_ok, forced_path, knobs
 from tiny_vllm_b200 import _lib
 from tiny_vllm_b200.quantization.cuda import apply_int8_weight_only_linear, select_path
 
@@ -81,24 +81,44 @@ def test_prefill_kernel_ragged_edges(M, N, K, dtype, bias):
 @pytest.mark.parametrize("M,N,K,dtype,bias", [(2500, 2056, 272, torch.bfloat16, True),
                                               (2305, 2304, 1024, torch.float16, False),
                                               (5000, 1024, 2048, torch.bfloat16, False)])
-def test_tensor_memory_weights_kernel(M, N, K, dtype, bias, monkeypatch):
-    # the prefill variant that keeps the expanded weights in tensor memory (default for K >= 2048),
+def test_tensor_memory_weights_kernel(M, N, K, dtype, bias):
+    # the variant that keeps the expanded weights in tensor memory (512 <= M < 1024 by default),
     # forced here for ragged M / N and a K tail as well
-    monkeypatch.setenv("B200Q_DEBUG_TS_MIN_K", "16")
-    assert select_path(_lib.OP_W8A16, M, N, K) == "umma_f16_tmem_weights_channels256"
-    q, s = O.make_weight(N, K, seed=N)
-    x = O.make_activation(M, K, seed=M, dtype=dtype, outliers=False)
-    b = (torch.randn(N, generator=torch.Generator().manual_seed(1)) * 0.1).to(dtype) if bias else None
-    y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda())
-    m = O.tensor_metrics(O.w8a16_native_reference(x, q, s, b), y)
-    assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
-    # every int8 code expands exactly: identity activations select weight columns
-    Kc, Mc, Nc = 256, 2560, 2048
-    qc = torch.stack([torch.roll(torch.arange(-128, 128, dtype=torch.int16).to(torch.int8), i)
-                      for i in range(Nc)])
-    xc = torch.eye(Kc, dtype=dtype).repeat(Mc // Kc, 1)
-    yc = apply_int8_weight_only_linear(xc.cuda(), qc.cuda(), torch.ones(Nc).cuda())
-    assert torch.equal(yc.float().cpu(), qc.float().T.repeat(Mc // Kc, 1))
+    with knobs(TS_MIN_K=16, W8A16_PAIR_MIN_M=1 << 30):
+        assert select_path(_lib.OP_W8A16, M, N, K) == "umma_f16_tmem_weights_channels256"
+        q, s = O.make_weight(N, K, seed=N)
+        x = O.make_activation(M, K, seed=M, dtype=dtype, outliers=False)
+        b = (torch.randn(N, generator=torch.Generator().manual_seed(1)) * 0.1).to(dtype) if bias else None
+        y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda())
+        m = O.tensor_metrics(O.w8a16_native_reference(x, q, s, b), y)
+        assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
+        # every int8 code expands exactly: identity activations select weight columns
+        Kc, Mc, Nc = 256, 2560, 2048
+        qc = torch.stack([torch.roll(torch.arange(-128, 128, dtype=torch.int16).to(torch.int8), i)
+                          for i in range(Nc)])
+        xc = torch.eye(Kc, dtype=dtype).repeat(Mc // Kc, 1)
+        yc = apply_int8_weight_only_linear(xc.cuda(), qc.cuda(), torch.ones(Nc).cuda())
+        assert torch.equal(yc.float().cpu(), qc.float().T.repeat(Mc // Kc, 1))
+    assert device_status_ok()
+
+
+@pytest.mark.parametrize("epilogue", [0, 1])
+@pytest.mark.parametrize("M,N,K,dtype,bias", [(2500, 2056, 272, torch.bfloat16, True),
+                                              (2305, 2304, 1024, torch.float16, False),
+                                              (5000, 1024, 2048, torch.bfloat16, False)])
+def test_expand_once_pair_kernel(M, N, K, dtype, bias, epilogue):
+    # prefill route: weights expanded to 16 bits once per call, then the CTA-pair kernel; both
+    # output routes of its epilogue, ragged M / N and a K tail
+    with knobs(PAIR_EPILOGUE=epilogue):
+        assert select_path(_lib.OP_W8A16, M, N, K) == "umma_f16_pair_expand_once_tokens256"
+        q, s = O.make_weight(N, K, seed=N)
+        x = O.make_activation(M, K, seed=M, dtype=dtype, outliers=False)
+        b = (torch.randn(N, generator=torch.Generator().manual_seed(1)) * 0.1).to(dtype) if bias else None
+        y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda())
+        m = O.tensor_metrics(O.w8a16_native_reference(x, q, s, b), y)
+        assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
+        m = O.tensor_metrics(O.w8a16_dequant_matmul(x, q, s, b), y)
+        assert m["relative_l2"] <= 1e-2 and m["cosine_similarity"] >= 0.9999, m
     assert device_status_ok()
 
 
@@ -163,7 +183,7 @@ def test_qwen3_8b_shapes(M, N, K):
                                               (300, 1024, 3072, torch.bfloat16, True),
                                               (200, 1000, 1040, torch.float16, True),
                                               (256, 4096, 1024, torch.bfloat16, False)])
-def test_cluster_split_k(M, N, K, dtype, bias, monkeypatch):
+def test_cluster_split_k(M, N, K, dtype, bias):
     # decode batches of 64-512 tokens: K is split over a cluster of 2 or 4 CTAs and the leader
     # adds the peers' partial tiles from its shared memory; ragged M, N and a K tail included
     q, s = O.make_weight(N, K, seed=N + K)
@@ -174,8 +194,8 @@ def test_cluster_split_k(M, N, K, dtype, bias, monkeypatch):
     m = O.tensor_metrics(O.w8a16_native_reference(x, q, s, b), y)
     assert m["relative_l2"] <= 4e-3 and m["cosine_similarity"] >= 0.9999, m
     assert torch.equal(bits(y), bits(apply_int8_weight_only_linear(*args)))     # deterministic
-    monkeypatch.setenv("B200Q_DEBUG_CLUSTER", "1")                              # same kernel, no cluster
-    y1 = apply_int8_weight_only_linear(*args)
+    with knobs(CLUSTER=1):                                                      # same kernel, no cluster
+        y1 = apply_int8_weight_only_linear(*args)
     assert O.tensor_metrics(y1, y)["relative_l2"] <= 2e-3
     assert device_status_ok()
 

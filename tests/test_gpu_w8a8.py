@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from oracle import quant_linear_oracle as O
-from gpu_util import bits, device_status_ok, forced_path
+from gpu_util import bits, device_status_ok, forced_path, knobs
 from tiny_vllm_b200 import _lib
 from tiny_vllm_b200.quantization.cuda import (apply_w8a8_linear, quantize_activation_int8,
                                               select_path, w8a8_int32_accumulators)
@@ -104,39 +104,63 @@ def test_quant_then_gemm_matches_reference_chain():
 
 @pytest.mark.parametrize("N,K", [(4096, 1024), (1024, 2048), (6144, 1024), (1024, 3072)])
 def test_baseline_prefill_shapes_full_size(N, K, oracle_c_lib):
-    # M = 8192 (the benchmark's workload).  Sampled rows are checked bit for bit against the
-    # integer oracle; all rows are checked through a size-independent property: the row sums
-    # of acc equal x_q @ (column sums of W) computed in int64.
+    # M = 8192 (the benchmark's workload), EVERY element: the CTA-pair kernel's raw int32
+    # accumulators against the integer oracle, its 16-bit output — through both
+    # output routes of its epilogue — against the oracle's restatement of the fused epilogue,
+    # and the single-CTA kernel's accumulators as the independent second implementation.
     M = 8192
     x, xq, a_s, q, s, _ = problem(M, N, K, seed=K)
-    gx, gq = xq.cuda(), q.cuda()
+    gx, gq, gas, gs = xq.cuda(), q.cuda(), a_s.cuda(), s.cuda()
+    assert select_path(_lib.OP_W8A8, M, N, K) == "umma_i8_pair_tokens256"
+    ref_acc = O.w8a8_int32_accumulators(xq, q)
     acc = w8a8_int32_accumulators(gx, gq)
+    assert torch.equal(acc.cpu(), ref_acc)
+    with knobs(NO_PAIR=1):
+        assert select_path(_lib.OP_W8A8, M, N, K) == "umma_i8_tokens128"
+        assert torch.equal(w8a8_int32_accumulators(gx, gq).cpu(), ref_acc)
+    # size-independent property: row sums of acc equal x_q @ (column sums of W) in int64
+    assert torch.equal(acc.to(torch.int64).sum(dim=1).cpu(), xq.to(torch.int64) @ q.to(torch.int64).sum(dim=0))
+    expect = bits(O.w8a8_native_epilogue(ref_acc, a_s, s, None, torch.bfloat16))
+    # default output route (TMA stores), then the st.global route the row-parallel scatter uses
+    for epilogue in (None, 0):
+        with knobs(**({} if epilogue is None else {"PAIR_EPILOGUE": epilogue})):
+            y = apply_w8a8_linear(gx, gas, gq, gs, out_dtype=torch.bfloat16)
+        assert torch.equal(bits(y.cpu()), expect), epilogue
     rows = torch.arange(0, M, 331)
-    assert torch.equal(acc[rows].cpu(), O.w8a8_int32_accumulators(xq[rows], q))
-    lhs = acc.to(torch.int64).sum(dim=1).cpu()
-    rhs = xq.to(torch.int64) @ q.to(torch.int64).sum(dim=0)
-    assert torch.equal(lhs, rhs)
-    y = apply_w8a8_linear(gx, a_s.cuda(), gq, s.cuda(), out_dtype=torch.bfloat16)
-    expect = O.w8a8_native_epilogue(acc[rows].cpu(), a_s[rows], s, None, torch.bfloat16)
-    assert torch.equal(bits(y[rows].cpu()), bits(expect))
     ref = O.w8a8_dequant_matmul(xq[rows], a_s[rows], q, s, None, torch.bfloat16)
     m = O.tensor_metrics(ref, y[rows])
     assert m["relative_l2"] <= REL_L2_GATE and m["cosine_similarity"] >= COSINE_GATE
     assert device_status_ok()
 
 
+@pytest.mark.parametrize("epilogue", [None, 0, 1])
 @pytest.mark.parametrize("M,N,K,dtype,bias", [(2500, 2056, 272, torch.bfloat16, True),
                                               (2305, 2304, 1024, torch.float16, False),
-                                              (9000, 520, 128, torch.bfloat16, False)])
-def test_cta_pair_kernel_ragged_edges(M, N, K, dtype, bias, oracle_c_lib):
+                                              (9000, 520, 128, torch.bfloat16, False),
+                                              (4700, 1288, 2064, torch.bfloat16, True)])
+def test_cta_pair_kernel_ragged_edges(M, N, K, dtype, bias, epilogue, oracle_c_lib):
     # shapes the CTA-pair (cta_group::2) kernel takes, with M not a multiple of 256 (the second
-    # CTA of the last pair is partly or wholly out of range), N not a multiple of 256 and a K tail
+    # CTA of the last pair is partly or wholly out of range), N not a multiple of 256 (nor of 16)
+    # and a K tail; every output route of the epilogue, and the raw accumulators
     assert select_path(_lib.OP_W8A8, M, N, K) == "umma_i8_pair_tokens256"
     x, xq, a_s, q, s, b = problem(M, N, K, seed=M, dtype=dtype, bias=bias)
-    y = apply_w8a8_linear(xq.cuda(), a_s.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda(),
-                          out_dtype=dtype)
-    expect = O.w8a8_native_epilogue(O.w8a8_int32_accumulators(xq, q), a_s, s, b, dtype)
+    ref_acc = O.w8a8_int32_accumulators(xq, q)
+    # None = the library's own choice (TMA stores)
+    with knobs(**({} if epilogue is None else {"PAIR_EPILOGUE": epilogue})):
+        y = apply_w8a8_linear(xq.cuda(), a_s.cuda(), q.cuda(), s.cuda(), None if b is None else b.cuda(),
+                              out_dtype=dtype)
+    expect = O.w8a8_native_epilogue(ref_acc, a_s, s, b, dtype)
     assert torch.equal(bits(y.cpu()), bits(expect))
+    if epilogue == 0:
+        assert torch.equal(w8a8_int32_accumulators(xq.cuda(), q.cuda()).cpu(), ref_acc)
+    assert device_status_ok()
+
+
+def test_cta_pair_raw_accumulators_with_odd_channel_count(oracle_c_lib):
+    # N % 4 != 0: the int32 rows are not 16-byte multiples, element-wise stores
+    M, N, K = 2400, 2051, 144
+    _, xq, _, q, _, _ = problem(M, N, K, seed=3)
+    assert torch.equal(w8a8_int32_accumulators(xq.cuda(), q.cuda()).cpu(), O.w8a8_int32_accumulators(xq, q))
     assert device_status_ok()
 
 
@@ -157,7 +181,7 @@ def test_baseline_decode_shapes(M, N, K, oracle_c_lib):
                                               (200, 1000, 1040, torch.float16, True),
                                               (100, 1000, 400, torch.bfloat16, False),
                                               (256, 4096, 1024, torch.bfloat16, False)])
-def test_cluster_split_k(M, N, K, dtype, bias, monkeypatch, oracle_c_lib):
+def test_cluster_split_k(M, N, K, dtype, bias, oracle_c_lib):
     # decode batches of 64-512 tokens: K is split over a cluster of 2 or 4 CTAs and the leader
     # adds the peers' int32 partial tiles from its shared memory: exact, so nothing may change
     x, xq, a_s, q, s, b = problem(M, N, K, seed=M + K, dtype=dtype, bias=bias)
@@ -167,8 +191,8 @@ def test_cluster_split_k(M, N, K, dtype, bias, monkeypatch, oracle_c_lib):
     assert torch.equal(w8a8_int32_accumulators(dev[0], dev[2]).cpu(), ref_acc)
     y = apply_w8a8_linear(*dev, bias=bd, out_dtype=dtype)
     assert torch.equal(bits(y.cpu()), bits(O.w8a8_native_epilogue(ref_acc, a_s, s, b, dtype)))
-    monkeypatch.setenv("B200Q_DEBUG_CLUSTER", "1")          # the same kernel without the cluster
-    assert torch.equal(bits(apply_w8a8_linear(*dev, bias=bd, out_dtype=dtype)), bits(y))
+    with knobs(CLUSTER=1):                                  # the same kernel without the cluster
+        assert torch.equal(bits(apply_w8a8_linear(*dev, bias=bd, out_dtype=dtype)), bits(y))
     assert device_status_ok()
 
 

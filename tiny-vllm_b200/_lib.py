@@ -40,6 +40,26 @@ PATH_UMMA = 2
 PATH_UMMA_SWAP = 3
 PATH_MMA_STREAM = 4
 
+# debug knobs (B200Q_KNOB_*): settings are private to the calling thread, unset at load
+KNOB_FORCE_PATH = 0
+KNOB_FLAGS = 1
+KNOB_BN = 2
+KNOB_SPLITS = 3
+KNOB_CLUSTER = 4
+KNOB_NO_PAIR = 5
+KNOB_NO_TS = 6
+KNOB_TS_MIN_K = 7
+KNOB_SIMT_MAX_M = 8
+KNOB_TILED_ONLY = 9
+KNOB_PAIR_EPILOGUE = 10
+KNOB_W8A16_PAIR_MIN_M = 11
+KNOB_NO_PDL = 12
+KNOB_WAIT_CYCLES = 13
+KNOB_PAIR_MIN_TILES = 14
+
+# B200Q_VERSION of include/b200q.h this binding was written for
+ABI_VERSION = 2
+
 # every symbol include/b200q.h declares: name -> (restype, argtypes)
 _c = ctypes
 SIGNATURES = {
@@ -60,6 +80,9 @@ SIGNATURES = {
     "b200q_device_status": (_c.c_int, []),
     "b200q_version": (_c.c_int, []),
     "b200q_debug_force_path": (_c.c_int, [_c.c_int]),
+    "b200q_debug_set": (_c.c_int, [_c.c_int, _c.c_int]),
+    "b200q_debug_reset": (None, []),
+    "b200q_check_status": (_c.c_int, [_c.POINTER(_c.c_int)]),
     "b200q_launch_count": (_c.c_uint64, []),
     "b200q_tp_allreduce": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_size_t,
                                       _c.c_int, _c.c_void_p]),
@@ -121,13 +144,32 @@ def lib() -> ctypes.CDLL:
                 raise RuntimeError(
                     f"{LIB_PATH} is missing: build it with `python tiny-vllm_b200/build.py` "
                     "(there is no fallback implementation)")
+            from . import build as _build
+            if not _build.is_current():
+                raise RuntimeError(
+                    f"{LIB_PATH} was not built from the current csrc/ and include/b200q.h "
+                    "(source hash differs): run `python tiny-vllm_b200/build.py`")
             handle = ctypes.CDLL(str(LIB_PATH))
             for name, (restype, argtypes) in SIGNATURES.items():
                 fn = getattr(handle, name)
                 fn.restype = restype
                 fn.argtypes = argtypes
+            if handle.b200q_version() != ABI_VERSION:
+                raise RuntimeError(
+                    f"{LIB_PATH} reports ABI version {handle.b200q_version()}, this binding expects "
+                    f"{ABI_VERSION}: rebuild with `python tiny-vllm_b200/build.py`")
             _lib = handle
     return _lib
+
+
+def check_device(where: str = "device status") -> None:
+    """Synchronous: reads and clears the device status word of the current device and raises
+    :class:`B200QError` (``ERR_DEVICE_TIMEOUT``) when a bounded device-side wait gave up since
+    the last read.  Call it after synchronising the stream."""
+    word = ctypes.c_int(0)
+    rc = lib().b200q_check_status(ctypes.byref(word))
+    if rc != OK:
+        raise B200QError(rc, where, f"status word 0x{word.value & 0xFFFFFFFF:x}")
 
 
 def check(code: int, where: str, detail: str = "") -> None:

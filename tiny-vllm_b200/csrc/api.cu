@@ -16,7 +16,13 @@ __device__ int g_device_status = 0;
 namespace {
 std::atomic<int> g_last_cuda_error{0};
 std::atomic<uint64_t> g_launches{0};
-std::atomic<int> g_forced_path{B200Q_PATH_AUTO};
+
+// Debug knobs of the calling thread (common.h): value and "is set" per knob.
+struct Knobs {
+  int value[B200Q_KNOB_COUNT];
+  bool set[B200Q_KNOB_COUNT];
+};
+thread_local Knobs t_knobs{};
 
 constexpr int kMaxDevices = 64;
 
@@ -68,7 +74,7 @@ int check_dims(int M, int N, int K) {
 // 7.3 vs 6.4 us for 1024 -> 6144).
 int auto_path_w8a8(int M, int N, int K) {
   (void)K;
-  if (M <= env_int("B200Q_DEBUG_SIMT_MAX_M", 0)) return B200Q_PATH_SIMT_STREAM;
+  if (M <= debug_knob(B200Q_KNOB_SIMT_MAX_M, 0)) return B200Q_PATH_SIMT_STREAM;
   if (M <= 32 || (M <= 48 && N <= 4096) || (M <= 64 && N <= 2048)) return B200Q_PATH_MMA_STREAM;
   return B200Q_PATH_UMMA;
 }
@@ -78,13 +84,13 @@ int auto_path_w8a8(int M, int N, int K) {
 // (M = 64: 7.2 vs 17.7 us for 2048 -> 1024, 12.4 vs 11.0 us for 1024 -> 6144).
 int auto_path_w8a16(int M, int N, int K) {
   (void)K;
-  if (M <= env_int("B200Q_DEBUG_SIMT_MAX_M", 0)) return B200Q_PATH_SIMT_STREAM;
+  if (M <= debug_knob(B200Q_KNOB_SIMT_MAX_M, 0)) return B200Q_PATH_SIMT_STREAM;
   if (M <= 48 || (M <= 64 && N <= 4096)) return B200Q_PATH_MMA_STREAM;
   return B200Q_PATH_UMMA;
 }
 
 int resolve_path(int op, int M, int N, int K) {
-  const int forced = g_forced_path.load();
+  const int forced = debug_knob(B200Q_KNOB_FORCE_PATH, B200Q_PATH_AUTO);
   if (forced != B200Q_PATH_AUTO) return forced;
   return op == B200Q_OP_W8A16 ? auto_path_w8a16(M, N, K) : auto_path_w8a8(M, N, K);
 }
@@ -125,9 +131,11 @@ int run_w8a8(GemmArgs& a) {
 
 }  // namespace
 
-bool pdl_enabled() {
-  static const bool on = env_int("B200Q_NO_PDL", 0) == 0;
-  return on;
+bool pdl_enabled() { return debug_knob(B200Q_KNOB_NO_PDL, 0) == 0; }
+
+int debug_knob(int knob, int dflt) {
+  if (knob < 0 || knob >= B200Q_KNOB_COUNT) return dflt;
+  return t_knobs.set[knob] ? t_knobs.value[knob] : dflt;
 }
 
 int sm_count() {
@@ -278,7 +286,7 @@ int b200q_w8a8_gemm_allreduce_tiled(const int8_t* xq, const float* a_scales, con
   a.status = d->status_ptr;
   a.stream = static_cast<cudaStream_t>(stream);
   // test hook: 1 = GEMM kernel only, 2 = sum-and-gather kernel only (two calls make one)
-  const int only = env_int("B200Q_DEBUG_TILED", 0);
+  const int only = debug_knob(B200Q_KNOB_TILED_ONLY, 0);
   if (!(only & 2)) {
     if (int rc = launch_w8a8_umma_pair_scatter(a, peer_stage, rank, world)) return rc;
   }
@@ -384,6 +392,7 @@ int b200q_w8a16_gemm(const void* x, const int8_t* qweight, const float* scales, 
     }
     return B200Q_OK;
   }
+  if (path == B200Q_PATH_UMMA && umma16_pair_applicable(M, N, K)) return launch_w8a16_umma_pair(a);
   if (path == B200Q_PATH_UMMA && umma16_ts_applicable(M, N, K)) return launch_w8a16_umma_ts(a);
   if (path == B200Q_PATH_UMMA || path == B200Q_PATH_UMMA_SWAP) {
     UmmaPlan plan;
@@ -396,8 +405,10 @@ int b200q_w8a16_gemm(const void* x, const int8_t* qweight, const float* scales, 
 
 size_t b200q_workspace_bytes(int op, int M, int N, int K) {
   if (op == B200Q_OP_W8A16 && check_dims(M, N, K) == B200Q_OK &&
-      resolve_path(op, M, N, K) == B200Q_PATH_UMMA && umma16_ts_applicable(M, N, K))
-    return 0;
+      resolve_path(op, M, N, K) == B200Q_PATH_UMMA) {
+    if (umma16_pair_applicable(M, N, K)) return umma16_pair_workspace_bytes(N, K);
+    if (umma16_ts_applicable(M, N, K)) return 0;
+  }
   if (op != B200Q_OP_W8A8 && op != B200Q_OP_W8A16) return 0;
   if (check_dims(M, N, K) != B200Q_OK) return 0;
   const int path = resolve_path(op, M, N, K);
@@ -422,6 +433,7 @@ const char* b200q_select_path(int op, int M, int N, int K) {
       return a16 ? "mma_stream_w8a16_splitk" : "mma_stream_s8_splitk";
     case B200Q_PATH_UMMA:
       if (!a16 && umma_pair_applicable(M, N, K, false)) return "umma_i8_pair_tokens256";
+      if (a16 && umma16_pair_applicable(M, N, K)) return "umma_f16_pair_expand_once_tokens256";
       if (a16 && umma16_ts_applicable(M, N, K)) return "umma_f16_tmem_weights_channels256";
       return a16 ? "umma_f16_expand_tokens128" : "umma_i8_tokens128";
     case B200Q_PATH_UMMA_SWAP:
@@ -477,12 +489,31 @@ int b200q_device_status(void) {
   return v;
 }
 
+int b200q_check_status(int* status_word) {
+  const int v = b200q_device_status();
+  if (status_word != nullptr) *status_word = v;
+  if (v < 0) return B200Q_ERR_LAUNCH;
+  return v == 0 ? B200Q_OK : B200Q_ERR_DEVICE_TIMEOUT;
+}
+
 int b200q_version(void) { return B200Q_VERSION; }
 
 int b200q_debug_force_path(int path) {
   if (path < B200Q_PATH_AUTO || path > B200Q_PATH_MMA_STREAM) return -1;
-  return g_forced_path.exchange(path);
+  const int prev = debug_knob(B200Q_KNOB_FORCE_PATH, B200Q_PATH_AUTO);
+  t_knobs.value[B200Q_KNOB_FORCE_PATH] = path;
+  t_knobs.set[B200Q_KNOB_FORCE_PATH] = path != B200Q_PATH_AUTO;
+  return prev;
 }
+
+int b200q_debug_set(int knob, int value) {
+  if (knob < 0 || knob >= B200Q_KNOB_COUNT) return -1;
+  t_knobs.value[knob] = value;
+  t_knobs.set[knob] = true;
+  return 0;
+}
+
+void b200q_debug_reset(void) { t_knobs = Knobs{}; }
 
 uint64_t b200q_launch_count(void) { return g_launches.load(); }
 

@@ -80,10 +80,25 @@ bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan);
 // Returns a B200Q_* code.
 int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan);
 
-// gemm_umma.cu: cached TMA descriptor of a dense row-major matrix viewed as bytes.
+// gemm_umma.cu: TMA descriptor of a dense row-major matrix viewed as bytes [rows, row_bytes],
+// box = box_bytes (128: 128-byte swizzle, 64: 64-byte swizzle) x box_rows, zero fill outside.
+// make_tensor_map encodes on every call (activations and outputs: their addresses change from
+// call to call); get_tensor_map keeps the result in a per-process cache (weights: same
+// address for the life of the model).
+bool make_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                     uint32_t box_bytes, CUtensorMap* out);
 bool get_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
                     uint32_t box_bytes, CUtensorMap* out);
-int env_int(const char* name, int dflt);
+
+// Test and tuning hooks (B200Q_KNOB_* of b200q.h).  Every knob is unset (the built-in
+// behaviour) until the CALLING THREAD sets it through b200q_debug_set(); nothing is read from
+// the environment, so a stray variable can never change what a kernel computes.
+int debug_knob(int knob, int dflt);
+// Limit of one wait on a peer GPU in SM cycles: about a second unless a test shortened it.
+inline long long peer_wait_limit_cycles() {
+  const int k = debug_knob(B200Q_KNOB_WAIT_CYCLES, 0);
+  return k > 0 ? static_cast<long long>(k) : 2000000000LL;
+}
 
 // gemm_umma_pair.cu: CTA-pair (cta_group::2) variant for prefill-sized W8A8 problems
 bool umma_pair_applicable(int M, int N, int K, bool raw_int32_out);
@@ -96,6 +111,12 @@ int launch_tp_reduce_gather(const void* stage, void* const* peer_y,
                             void* const* peer_ctl, int rank, int world, int M, int N, int dtype,
                             cudaStream_t stream);
 
+// gemm_umma_pair.cu: W8A16 prefill route — weights expanded once per call into the
+// workspace, then the 16-bit CTA-pair kernel
+bool umma16_pair_applicable(int M, int N, int K);
+size_t umma16_pair_workspace_bytes(int N, int K);
+int launch_w8a16_umma_pair(const GemmArgs& a);
+
 // gemm_umma_w8a16.cu
 bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan);
 int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan);
@@ -107,7 +128,7 @@ int launch_w8a16_umma_ts(const GemmArgs& a);
 // Launches `kernel` so that it may overlap its start-up (barrier set-up, TMEM allocation,
 // descriptor prefetch, launch latency) with the tail of the previous kernel in the stream
 // (programmatic dependent launch).  Only for kernels that call ptx::grid_dependency_wait()
-// before their first access to global memory.  B200Q_NO_PDL=1 turns the overlap off.
+// before their first access to global memory.  B200Q_KNOB_NO_PDL turns the overlap off.
 bool pdl_enabled();
 template <typename... KArgs, typename... Args>
 cudaError_t launch_clustered(int cluster, bool overlap, void (*kernel)(KArgs...), dim3 grid,

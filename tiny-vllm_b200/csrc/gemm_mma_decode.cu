@@ -58,6 +58,7 @@ struct FuseParams {
   unsigned int* ctl[8]; // every rank's control words (only the own rank's are used)
   size_t half_bytes;    // bytes of one parity half
   int rank, world;
+  long long wait_limit; // SM cycles one wait on a peer may take
 };
 
 
@@ -104,7 +105,7 @@ __device__ __forceinline__ void exchange_and_sum(const OutT* part, const FusePar
       if (r == fp.rank) {
         w = part_w[wi];
       } else {
-        if (!wait_word8(mine + r * slot_words + off, epoch, &w)) ok = false;
+        if (!wait_word8(mine + r * slot_words + off, epoch, &w, fp.wait_limit)) ok = false;
       }
       if (kBf16) {
         lo += __uint_as_float(w << 16);
@@ -514,6 +515,7 @@ static int make_fuse_params(const GemmArgs& a, void* const* peer_recv, void* con
   fp->half_bytes = half;
   fp->rank = rank;
   fp->world = world;
+  fp->wait_limit = peer_wait_limit_cycles();
   return B200Q_OK;
 }
 

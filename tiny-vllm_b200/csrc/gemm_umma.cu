@@ -397,9 +397,27 @@ struct MapKeyHash {
 
 }  // namespace
 
-// Tensor map of a dense row-major matrix viewed as bytes [rows, row_bytes]: box =
-// box_bytes x box_rows with box_bytes = 128 (128-byte swizzle) or 64 (64-byte swizzle),
-// zero fill outside the matrix.  Cached: encoding costs microseconds.
+bool make_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                     uint32_t box_bytes, CUtensorMap* out) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {box_bytes, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    note_cuda_error(cudaErrorInvalidValue);
+    return false;
+  }
+  return true;
+}
+
+// Cached variant for matrices that keep their address (weights): encoding costs about a
+// microsecond of host time.
 bool get_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
                     uint32_t box_bytes, CUtensorMap* out) {
   static std::mutex mu;
@@ -415,21 +433,8 @@ bool get_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_
       return true;
     }
   }
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return false;
-  cuuint64_t dims[2] = {row_bytes, rows};
-  cuuint64_t strides[1] = {row_bytes};
-  cuuint32_t box[2] = {box_bytes, box_rows};
-  cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
-  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    note_cuda_error(cudaErrorInvalidValue);
-    return false;
-  }
+  if (!make_tensor_map(base, rows, row_bytes, box_rows, box_bytes, &m)) return false;
   {
     std::lock_guard<std::mutex> g(mu);
     if (cache.size() > 8192) cache.clear();
@@ -437,12 +442,6 @@ bool get_tensor_map(const void* base, uint64_t rows, uint64_t row_bytes, uint32_
   }
   *out = m;
   return true;
-}
-
-int env_int(const char* name, int dflt) {
-  const char* s = std::getenv(name);
-  if (s == nullptr || *s == '\0') return dflt;
-  return std::atoi(s);
 }
 
 namespace {
@@ -499,7 +498,7 @@ bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan) {
       }
     }
   }
-  bn = env_int("B200Q_DEBUG_BN", bn);
+  bn = debug_knob(B200Q_KNOB_BN, bn);
   if (bn < 32 || bn > 256 || (bn % 32) != 0) return false;
   pl.bn = bn;
   pl.tiles_a = (pl.rows_a + kTileA - 1) / kTileA;
@@ -515,7 +514,7 @@ bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan) {
     splits = std::min(splits, pl.k_blocks / 32);
     splits = std::min(splits, 8);
   }
-  splits = env_int("B200Q_DEBUG_SPLITS", splits);
+  splits = debug_knob(B200Q_KNOB_SPLITS, splits);
   if (splits < 1) splits = 1;
   if (splits > pl.k_blocks) splits = pl.k_blocks;
   pl.kb_per_split = (pl.k_blocks + splits - 1) / splits;
@@ -535,7 +534,7 @@ bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan) {
         cl = cand;
         break;
       }
-    cl = env_int("B200Q_DEBUG_CLUSTER", cl);
+    cl = debug_knob(B200Q_KNOB_CLUSTER, cl);
     if (cl == 2 || cl == 4) {
       const int per = (pl.k_blocks + cl - 1) / cl;
       if (tiles * cl <= sms && per * (cl - 1) < pl.k_blocks) {
@@ -573,8 +572,11 @@ int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
   const void* base_a = plan.swap ? static_cast<const void*>(a.w) : a.x;
   const void* base_b = plan.swap ? a.x : static_cast<const void*>(a.w);
   CUtensorMap ta, tb;
-  if (!get_tensor_map(base_a, plan.rows_a, a.K, kTileA, kBlockK, &ta)) return B200Q_ERR_LAUNCH;
-  if (!get_tensor_map(base_b, plan.rows_b, a.K, plan.bn, kBlockK, &tb)) return B200Q_ERR_LAUNCH;
+  // the weight map is cached (fixed address), the activation map is encoded per call
+  const auto map_a = plan.swap ? get_tensor_map : make_tensor_map;
+  const auto map_b = plan.swap ? make_tensor_map : get_tensor_map;
+  if (!map_a(base_a, plan.rows_a, a.K, kTileA, kBlockK, &ta)) return B200Q_ERR_LAUNCH;
+  if (!map_b(base_b, plan.rows_b, a.K, plan.bn, kBlockK, &tb)) return B200Q_ERR_LAUNCH;
   // Prefill orientation, 16-bit output, no split-K: outputs are transposed through shared
   // memory so that every store instruction writes complete 128-byte lines.
   const bool fast_store = !plan.swap && a.acc_out == nullptr &&
@@ -607,7 +609,7 @@ int launch_w8a8_umma(const GemmArgs& a, const UmmaPlan& plan) {
                     : nullptr;
   kp.status = a.status;
   kp.fast_store = fast_store ? 1 : 0;
-  kp.debug_flags = env_int("B200Q_DEBUG_FLAGS", 0);
+  kp.debug_flags = debug_knob(B200Q_KNOB_FLAGS, 0);
 
   cudaError_t e;
   if (a.acc_out != nullptr) {

@@ -448,7 +448,7 @@ bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan) {
       }
     }
   }
-  bn = env_int("B200Q_DEBUG_BN", bn);
+  bn = debug_knob(B200Q_KNOB_BN, bn);
   if (bn < 32 || bn > 256 || (bn % 32) != 0) return false;
   pl.bn = bn;
   pl.tiles_a = (pl.rows_a + kTileA - 1) / kTileA;
@@ -464,7 +464,7 @@ bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan) {
     splits = std::min(splits, pl.k_blocks / 64);
     splits = std::min(splits, 8);
   }
-  splits = env_int("B200Q_DEBUG_SPLITS", splits);
+  splits = debug_knob(B200Q_KNOB_SPLITS, splits);
   if (splits < 1) splits = 1;
   if (splits > pl.k_blocks) splits = pl.k_blocks;
   pl.kb_per_split = (pl.k_blocks + splits - 1) / splits;
@@ -481,7 +481,7 @@ bool umma16_make_plan(int M, int N, int K, int swap, UmmaPlan* plan) {
         cl = cand;
         break;
       }
-    cl = env_int("B200Q_DEBUG_CLUSTER", cl);
+    cl = debug_knob(B200Q_KNOB_CLUSTER, cl);
     if (cl == 2 || cl == 4) {
       const int per = (pl.k_blocks + cl - 1) / cl;
       if (tiles * cl <= sms && per * (cl - 1) < pl.k_blocks) {
@@ -527,7 +527,7 @@ int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan) {
   const int rows8 = plan.swap ? kTileA : plan.bn;
   CUtensorMap tx, tw;
   // activations: [M, 2K bytes], 128-byte boxes; weights: [N, K bytes], 64-byte boxes
-  if (!get_tensor_map(a.x, a.M, static_cast<uint64_t>(a.K) * 2, rows16, kRow16, &tx))
+  if (!make_tensor_map(a.x, a.M, static_cast<uint64_t>(a.K) * 2, rows16, kRow16, &tx))
     return B200Q_ERR_LAUNCH;
   if (!get_tensor_map(a.w, a.N, a.K, rows8, kRow8, &tw)) return B200Q_ERR_LAUNCH;
 
@@ -558,7 +558,7 @@ int launch_w8a16_umma(const GemmArgs& a, const UmmaPlan& plan) {
   kp.status = a.status;
   kp.fast_store = (!plan.swap && (plan.splits == 1 || plan.cluster > 1) && (a.N % 8) == 0 &&
                    (plan.bn % 64) == 0) ? 1 : 0;
-  kp.debug_flags = env_int("B200Q_DEBUG_FLAGS", 0);
+  kp.debug_flags = debug_knob(B200Q_KNOB_FLAGS, 0);
 
   cudaError_t e;
   if (plan.cluster > 1) {

@@ -330,8 +330,8 @@ cudaError_t launch_ts(const CUtensorMap& tx, const CUtensorMap& tw, const TsPara
 // 84.3 vs 87.1 us, 2048 -> 1024 44.8 vs 49.9 us, 1024 -> 6144 128.4 vs 131.5 us, 3072 -> 1024
 // 61.6 vs 71.3 us.
 bool umma16_ts_applicable(int M, int N, int K) {
-  if (env_int("B200Q_DEBUG_NO_TS", 0) != 0) return false;
-  if (K < env_int("B200Q_DEBUG_TS_MIN_K", 1024)) return false;
+  if (debug_knob(B200Q_KNOB_NO_TS, 0) != 0) return false;
+  if (K < debug_knob(B200Q_KNOB_TS_MIN_K, 1024)) return false;
   if ((K % 16) != 0 || (N % 8) != 0) return false;   // 16-byte output pieces
   const long long tiles = static_cast<long long>((N + kTsChannels - 1) / kTsChannels) *
                           ((M + kTsTokens - 1) / kTsTokens);
@@ -340,7 +340,7 @@ bool umma16_ts_applicable(int M, int N, int K) {
 
 int launch_w8a16_umma_ts(const GemmArgs& a) {
   CUtensorMap tx, tw;
-  if (!get_tensor_map(a.x, a.M, static_cast<uint64_t>(a.K) * 2, kTsTokens, kRow16, &tx))
+  if (!make_tensor_map(a.x, a.M, static_cast<uint64_t>(a.K) * 2, kTsTokens, kRow16, &tx))
     return B200Q_ERR_LAUNCH;
   if (!get_tensor_map(a.w, a.N, a.K, kTsChannels, kRow8, &tw)) return B200Q_ERR_LAUNCH;
   TsParams tp{};
@@ -355,7 +355,7 @@ int launch_w8a16_umma_ts(const GemmArgs& a) {
   tp.bias = a.bias;
   tp.out = a.y;
   tp.status = a.status;
-  tp.debug_flags = env_int("B200Q_DEBUG_FLAGS", 0);
+  tp.debug_flags = debug_knob(B200Q_KNOB_FLAGS, 0);
   const long long items = static_cast<long long>(tp.tiles_ch) * tp.tiles_tok;
   const int grid = static_cast<int>(std::min<long long>(items, sm_count()));
   cudaError_t e = a.dtype == B200Q_DTYPE_BF16 ? launch_ts<__nv_bfloat16>(tx, tw, tp, grid, a.stream)

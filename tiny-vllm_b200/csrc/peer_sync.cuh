@@ -9,7 +9,9 @@
 
 namespace b200q {
 
-constexpr long long kSpinLimitCycles = 2000000000LL;  // about one second
+// Default limit of one wait on a peer, in SM cycles (about one second).  The launchers pass
+// the limit to the kernels as a parameter, so that a test can shorten it to milliseconds.
+constexpr long long kSpinLimitCycles = 2000000000LL;
 
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -36,10 +38,11 @@ __device__ __forceinline__ void st_peer16(void* p, const uint4 v) {
 }
 
 // Waits until the flag holds at least `epoch` (wrap-safe).  False when the limit ran out.
-__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int epoch) {
+__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int epoch,
+                                          long long limit_cycles) {
   const long long t0 = clock64();
   while (static_cast<int>(ld_acquire_sys(flag) - epoch) < 0) {
-    if (clock64() - t0 > kSpinLimitCycles) return false;
+    if (clock64() - t0 > limit_cycles) return false;
   }
   return true;
 }
@@ -104,13 +107,14 @@ __device__ __forceinline__ uint2 ld_word8(const void* p) {
   return v;
 }
 // Polls a tagged word until it carries `epoch`; false when the limit ran out.
-__device__ __forceinline__ bool wait_word8(const void* p, uint32_t epoch, uint32_t* data) {
+__device__ __forceinline__ bool wait_word8(const void* p, uint32_t epoch, uint32_t* data,
+                                           long long limit_cycles) {
   uint2 v = ld_word8(p);
   if (v.y != epoch) {
     const long long t0 = clock64();
     do {
       v = ld_word8(p);
-    } while (v.y != epoch && clock64() - t0 < kSpinLimitCycles);
+    } while (v.y != epoch && clock64() - t0 < limit_cycles);
   }
   *data = v.x;
   return v.y == epoch;

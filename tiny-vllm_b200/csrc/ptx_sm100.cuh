@@ -86,6 +86,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
       : "memory");
 }
 
+// Hint: bring one box of the tensor into L2 (no shared-memory destination, no completion).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tmap, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+               ::"l"(tmap), "r"(c0), "r"(c1)
+               : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -317,6 +324,17 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
                : "memory");
 }
 
+// The same with ONE instruction for both CTAs of the pair: the arrival is delivered to the
+// mbarrier at this shared-memory offset in every CTA of cta_mask (bit r = cluster rank r).
+// Only the signal is multicast; no data moves.
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t own_bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(own_bar), "h"(mask)
+      : "memory");
+}
+
 // D (256 x N, rows 0-127 in this CTA's TMEM, 128-255 in the peer's) (+)= A * B^T with A
 // and B halves taken from both CTAs' shared memory at the same offsets.
 __device__ __forceinline__ void umma_i8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
@@ -329,6 +347,45 @@ __device__ __forceinline__ void umma_i8_ss_pair(uint32_t d_tmem, uint64_t a_desc
       "}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// The same for 16-bit operands (bf16 or fp16 per the instruction descriptor), fp32 accumulators.
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// ------------------------------------------------- TMA store (shared -> global), bulk groups
+// 2-D tiled store of one box from this CTA's shared memory to THIS GPU's global memory.  c0 is
+// the innermost coordinate (c0 * element size a multiple of 16 bytes); neither coordinate may
+// be negative.  The part of the box outside the tensor is not written.  The writes to shared
+// memory that filled the box must be followed by fence_proxy_async_smem() before this call.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t smem_src, int c0,
+                                             int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tmap), "r"(smem_src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Returns when at most N of this thread's committed bulk groups still READ their shared-memory
+// source (the source may be overwritten afterwards; the global writes may still be in flight).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Returns when at most N of this thread's committed bulk groups are incomplete.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // Named barrier among a subset of the CTA's warps.

@@ -39,6 +39,7 @@ struct Params {
   unsigned long long n_chunks;  // 16-byte chunks in the tensor
   int is_bf16;
   int* status;
+  long long wait_limit;  // SM cycles one wait on a peer may take
 };
 
 // W = compile-time bound on the number of ranks, U = chunks per thread per iteration: all
@@ -60,7 +61,7 @@ tp_allreduce_kernel(const Params p) {
   // ---- barrier A: every rank's partial result is complete
   if (threadIdx.x < p.world) {
     if (blockIdx.x == 0) st_release_sys(p.pad[threadIdx.x] + kSlotA + p.rank, epoch);
-    if (!wait_flag(my_pad + kSlotA + threadIdx.x, epoch)) s_flag = 1;
+    if (!wait_flag(my_pad + kSlotA + threadIdx.x, epoch, p.wait_limit)) s_flag = 1;
   }
   __syncthreads();
   const bool ok = s_flag == 0;
@@ -107,7 +108,7 @@ tp_allreduce_kernel(const Params p) {
     const unsigned int done = atomicAdd(my_pad + kSlotCounter, 1u);
     if (done == gridDim.x - 1) {
       my_pad[kSlotCounter] = 0u;
-      if (s_flag == 0) s_flag = 2;
+      s_flag = s_flag == 0 ? 2 : 3;  // 3: this CTA's own wait gave up
     }
   }
   __syncthreads();
@@ -115,14 +116,16 @@ tp_allreduce_kernel(const Params p) {
     __threadfence_system();
     if (threadIdx.x < p.world) {
       st_release_sys(p.pad[threadIdx.x] + kSlotB + p.rank, epoch);
-      if (!wait_flag(my_pad + kSlotB + threadIdx.x, epoch)) atomicCAS(p.status, 0, 0x502);
+      if (!wait_flag(my_pad + kSlotB + threadIdx.x, epoch, p.wait_limit)) atomicCAS(p.status, 0, 0x502);
     }
     __syncthreads();
     if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
-  } else if (s_flag == 1 && threadIdx.x == 0) {
+  } else if (s_flag != 0 && threadIdx.x == 0) {
     atomicCAS(p.status, 0, 0x501);
-    // keep the call count in step with the peers even though this call failed
-    if (blockIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
+    // Keep the call count in step with the peers even though this call failed.  Only the
+    // rank's LAST CTA may do it: every CTA reads the count at its start to learn the call
+    // number, so it must not change while a CTA of this launch may still be starting.
+    if (s_flag == 3) *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
   }
 }
 
@@ -174,7 +177,7 @@ tp_allreduce_multimem_kernel(const Params p, uint4* __restrict__ mc) {
   const unsigned int epoch = s_epoch;
   if (threadIdx.x < p.world) {
     if (blockIdx.x == 0) st_release_sys(p.pad[threadIdx.x] + kSlotA + p.rank, epoch);
-    if (!wait_flag(my_pad + kSlotA + threadIdx.x, epoch)) s_flag = 1;
+    if (!wait_flag(my_pad + kSlotA + threadIdx.x, epoch, p.wait_limit)) s_flag = 1;
   }
   __syncthreads();
   if (s_flag == 0) {
@@ -204,7 +207,7 @@ tp_allreduce_multimem_kernel(const Params p, uint4* __restrict__ mc) {
     const unsigned int done = atomicAdd(my_pad + kSlotCounter, 1u);
     if (done == gridDim.x - 1) {
       my_pad[kSlotCounter] = 0u;
-      if (s_flag == 0) s_flag = 2;
+      s_flag = s_flag == 0 ? 2 : 3;  // 3: this CTA's own wait gave up
     }
   }
   __syncthreads();
@@ -212,13 +215,14 @@ tp_allreduce_multimem_kernel(const Params p, uint4* __restrict__ mc) {
     __threadfence_system();
     if (threadIdx.x < p.world) {
       st_release_sys(p.pad[threadIdx.x] + kSlotB + p.rank, epoch);
-      if (!wait_flag(my_pad + kSlotB + threadIdx.x, epoch)) atomicCAS(p.status, 0, 0x505);
+      if (!wait_flag(my_pad + kSlotB + threadIdx.x, epoch, p.wait_limit)) atomicCAS(p.status, 0, 0x505);
     }
     __syncthreads();
     if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
-  } else if (s_flag == 1 && threadIdx.x == 0) {
+  } else if (s_flag != 0 && threadIdx.x == 0) {
     atomicCAS(p.status, 0, 0x504);
-    if (blockIdx.x == 0) *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
+    // only the rank's last CTA moves the call count (see tp_allreduce_kernel)
+    if (s_flag == 3) *reinterpret_cast<volatile unsigned int*>(my_pad + kSlotEpoch) = epoch;
   }
 }
 
@@ -247,7 +251,7 @@ tp_allreduce_pull_kernel(const Params p, uint4* __restrict__ out) {
   const unsigned int epoch = s_epoch;
   if (threadIdx.x < p.world) {
     if (blockIdx.x == 0) st_release_sys(p.pad[threadIdx.x] + kSlotA + p.rank, epoch);
-    if (!wait_flag(my_pad + kSlotA + threadIdx.x, epoch)) s_flag = 1;
+    if (!wait_flag(my_pad + kSlotA + threadIdx.x, epoch, p.wait_limit)) s_flag = 1;
   }
   __syncthreads();
   if (s_flag == 0) {
@@ -304,6 +308,7 @@ struct OneTripParams {
   unsigned long long n_chunks;
   int rank, world;
   int* status;
+  long long wait_limit;
 };
 
 template <bool BF16>
@@ -345,10 +350,10 @@ tp_allreduce_onetrip_kernel(const OneTripParams p) {
       uint4 v = own;
       if (r != p.rank) {
         const uint2* src = mine + r * slot_words + c * 4;
-        ok &= wait_word8(src + 0, epoch, &v.x);
-        ok &= wait_word8(src + 1, epoch, &v.y);
-        ok &= wait_word8(src + 2, epoch, &v.z);
-        ok &= wait_word8(src + 3, epoch, &v.w);
+        ok &= wait_word8(src + 0, epoch, &v.x, p.wait_limit);
+        ok &= wait_word8(src + 1, epoch, &v.y, p.wait_limit);
+        ok &= wait_word8(src + 2, epoch, &v.z, p.wait_limit);
+        ok &= wait_word8(src + 3, epoch, &v.w, p.wait_limit);
       }
       accumulate<BF16>(acc, v);
     }
@@ -380,6 +385,7 @@ struct GatherParams {
   int rank, world;
   int rows_per_owner, N, tiles_b;
   int* status;
+  long long wait_limit;
 };
 
 // W = compile-time bound on the number of ranks, U = chunks per thread in flight (U * W loads
@@ -405,7 +411,7 @@ tp_reduce_gather_kernel(const GatherParams p) {
   // every rank's scatter GEMM has completed (stream order on the sender, one flag per peer)
   if (threadIdx.x < p.world) {
     if (blockIdx.x == 0) st_release_sys(p.ctl[threadIdx.x] + kCtlReady + p.rank, epoch);
-    if (!wait_flag(ctl + kCtlReady + threadIdx.x, epoch)) s_flag = 1;
+    if (!wait_flag(ctl + kCtlReady + threadIdx.x, epoch, p.wait_limit)) s_flag = 1;
   }
   __syncthreads();
   const bool ready = s_flag == 0;
@@ -457,7 +463,7 @@ tp_reduce_gather_kernel(const GatherParams p) {
     __threadfence_system();
     if (threadIdx.x < p.world) {
       st_release_sys(p.ctl[threadIdx.x] + kCtlDone + p.rank, epoch);
-      if (!wait_flag(ctl + kCtlDone + threadIdx.x, epoch)) atomicCAS(p.status, 0, 0x702);
+      if (!wait_flag(ctl + kCtlDone + threadIdx.x, epoch, p.wait_limit)) atomicCAS(p.status, 0, 0x702);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -486,6 +492,7 @@ int launch_tp_reduce_gather(const void* stage, void* const* peer_y,
   p.N = N;
   p.tiles_b = (N + 255) / 256;
   p.status = device_status_ptr();
+  p.wait_limit = peer_wait_limit_cycles();
   if (p.status == nullptr) return B200Q_ERR_LAUNCH;
   const int n_tiles = (p.rows_per_owner / 128) * p.tiles_b;
   const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
@@ -531,6 +538,7 @@ extern "C" int b200q_tp_allreduce(void* const* peer_buffers, void* const* peer_f
   p.n_chunks = n_elems / 8;
   p.is_bf16 = dtype == B200Q_DTYPE_BF16;
   p.status = device_status_ptr();
+  p.wait_limit = peer_wait_limit_cycles();
   if (p.status == nullptr) return B200Q_ERR_LAUNCH;
   const unsigned long long per_rank = (p.n_chunks + world - 1) / world;
   long long blocks = static_cast<long long>((per_rank + kThreads * 4 - 1) / (kThreads * 4));
@@ -586,6 +594,7 @@ extern "C" int b200q_tp_allreduce_small(const void* x, void* y, size_t n_elems, 
   p.rank = rank;
   p.world = world;
   p.status = device_status_ptr();
+  p.wait_limit = peer_wait_limit_cycles();
   if (p.status == nullptr) return B200Q_ERR_LAUNCH;
   // one chunk per thread until every SM has a CTA; never more CTAs than are resident at once
   long long blocks = static_cast<long long>((p.n_chunks + kThreads - 1) / kThreads);
@@ -629,6 +638,7 @@ extern "C" int b200q_tp_allreduce_pull(void* const* peer_buffers, void* const* p
   p.n_chunks = n_elems / 8;
   p.is_bf16 = dtype == B200Q_DTYPE_BF16;
   p.status = device_status_ptr();
+  p.wait_limit = peer_wait_limit_cycles();
   if (p.status == nullptr) return B200Q_ERR_LAUNCH;
   long long blocks = static_cast<long long>((p.n_chunks + kThreads * 4 - 1) / (kThreads * 4));
   if (blocks < 1) blocks = 1;
@@ -676,6 +686,7 @@ extern "C" int b200q_tp_allreduce_multimem(void* multicast_buffer, void* const* 
   p.n_chunks = n_elems / 8;
   p.is_bf16 = dtype == B200Q_DTYPE_BF16;
   p.status = device_status_ptr();
+  p.wait_limit = peer_wait_limit_cycles();
   if (p.status == nullptr) return B200Q_ERR_LAUNCH;
   const unsigned long long per_rank = (p.n_chunks + world - 1) / world;
   long long blocks = static_cast<long long>((per_rank + kThreads * 4 - 1) / (kThreads * 4));
