@@ -357,6 +357,36 @@ int b200q_tp_allreduce_small(const void* x, void* y, size_t n_elems, int dtype,
                              size_t recv_bytes, int rank, int world, void* stream);
 
 /*
+ * The exchange step after a row-parallel linear fused with its consumers: replaces the chain
+ *   dist.all_reduce(y)                         (nanovllm/layers/linear.py:274-275)
+ *   x, residual = RMSNorm(y, residual)         (nanovllm/layers/layernorm.py:28-40, called at
+ *                                               nanovllm/models/qwen3.py:160-166)
+ *   x_q, a_scales = quantize_int8_per_row_dynamic(x)   (nanovllm/quantization/w8a8.py:21-23)
+ * by ONE kernel per rank.  Rank r owns token rows [r * M / world, (r + 1) * M / world): it
+ * sums the partial outputs of all ranks for those rows (fp32, rank order, one rounding to the
+ * 16-bit type: the tensor the all-reduce would have produced), adds its shard of the residual
+ * stream, writes the new residual shard, applies RMSNorm, quantises, and writes the int8 codes
+ * and fp32 scales of its rows into EVERY rank's code / scale buffer, which then hold the whole
+ * [M, K] input of the next W8A8 layer.  The residual stream stays sharded by rows: no rank
+ * ever needs another rank's rows of it.  Codes, scales and residual are bit-identical to
+ * b200q_tp_allreduce followed by b200q_add_rmsnorm_quant_i8 on the owned rows.
+ *
+ * peer_partials / peer_flag_pads / peer_xq / peer_scales are HOST arrays of `world` DEVICE
+ * addresses as mapped into the calling process: rank r's partial output [M, K] (dtype),
+ * flag pad (the pads of b200q_tp_allreduce: shared call numbering), code buffer int8 [M, K]
+ * and scale buffer fp32 [M] (symmetric allocations).  residual_in (may be NULL) / residual_out
+ * (may be NULL, may alias residual_in) / y_local (normalised rows, may be NULL) are LOCAL
+ * tensors of M / world rows; weight is [K].  M % world == 0, K % 16 == 0, K <= 16384.  Every
+ * rank makes the same sequence of calls.  A wait that runs out sets device status 0x801 /
+ * 0x802.  No counterpart in the reference, which runs the three steps one after another.
+ */
+int b200q_tp_reduce_rmsnorm_quant(void* const* peer_partials, void* const* peer_flag_pads,
+                                  const void* residual_in, void* residual_out, const void* weight,
+                                  float eps, void* const* peer_xq, void* const* peer_scales,
+                                  void* y_local, int M, int K, int rank, int world, int dtype,
+                                  void* stream);
+
+/*
  * W8A8 linear for callers that have no way to hand over scratch memory.
  * (No counterpart in the reference: its kernels never need scratch.)
  *

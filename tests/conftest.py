@@ -49,6 +49,44 @@ def golden_cases():
     return load_golden_cases()
 
 
+def load_fused_producer_cases():
+    """(norm cases, activation cases) of tests/golden/fused_producers_golden.npz: outputs of the
+    reference's RMSNorm / SiluAndMul modules."""
+    z = np.load(ROOT / "tests" / "golden" / "fused_producers_golden.npz")
+    norm, silu = [], []
+    for i in range(int(z["n_norm"])):
+        p = f"n{i}_"
+        dt = getattr(torch, str(z[p + "dtype"]))
+        M, K = (int(v) for v in z[p + "shape"])
+        res = z[p + "res"]
+        norm.append({"id": i, "M": M, "K": K, "dtype": dt, "eps": float(z["eps"]),
+                     "x": _from_bits16(z[p + "x"], dt).view(M, K),
+                     "res": _from_bits16(res, dt).view(M, K) if res.size else None,
+                     "w": _from_bits16(z[p + "w"], dt),
+                     "y": _from_bits16(z[p + "y"], dt).view(M, K),
+                     "new_res": _from_bits16(z[p + "new_res"], dt).view(M, K) if res.size else None})
+    for i in range(int(z["n_silu"])):
+        p = f"s{i}_"
+        dt = getattr(torch, str(z[p + "dtype"]))
+        M, inter = (int(v) for v in z[p + "shape"])
+        silu.append({"id": i, "M": M, "I": inter, "dtype": dt,
+                     "gate_up": _from_bits16(z[p + "gate_up"], dt).view(M, 2 * inter),
+                     "y": _from_bits16(z[p + "y"], dt).view(M, inter)})
+    return norm, silu
+
+
+@pytest.fixture(scope="session")
+def fused_producer_cases():
+    return load_fused_producer_cases()
+
+
+@pytest.fixture(scope="session")
+def baseline_shape_golden():
+    """Reference results at the benchmark's shape families (digests, sampled rows)."""
+    z = np.load(ROOT / "tests" / "golden" / "baseline_shapes_golden.npz")
+    return {k: z[k] for k in z.files}
+
+
 @pytest.fixture(scope="session")
 def oracle_c_lib():
     """Builds the C part of the oracle (gcc) once per session."""

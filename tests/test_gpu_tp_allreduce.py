@@ -459,34 +459,129 @@ def _tiled_worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
+def _exchange_worker(rank, world, port, out_dir):
+    """Fused exchange (reduce + residual add + RMSNorm + quantise + gather of codes) against the
+    two-kernel route all-reduce -> b200q_add_rmsnorm_quant_i8, then the chain a layer runs:
+    row-parallel W8A8 GEMM -> exchange -> column-parallel W8A8 GEMM on the gathered codes."""
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import tiny_vllm_b200  # noqa: F401
+    from tiny_vllm_b200 import _lib
+    from tiny_vllm_b200.layers.tp_comm import PeerAllReduce
+    from tiny_vllm_b200.quantization.cuda import add_rmsnorm_quantize_int8
+    ok, notes = True, []
+    try:
+        comm = PeerAllReduce(max_bytes=16 << 20)
+        for call, (M, K, dtype, with_res) in enumerate([(8192, 1024, torch.bfloat16, True),
+                                                        (64, 1024, torch.bfloat16, True),
+                                                        (8 * world, 2048, torch.float16, False),
+                                                        (8192, 1024, torch.bfloat16, True)]):
+            g = torch.Generator().manual_seed(900 + call)
+            parts = [(torch.randn(M, K, generator=g) * 1.5).to(dtype) for _ in range(world)]
+            residual = (torch.randn(M, K, generator=g) * 2).to(dtype) if with_res else None
+            weight = (1.0 + 0.2 * torch.randn(K, generator=g)).to(dtype).cuda()
+            rows = M // world
+            # two-kernel route
+            t = comm.buffer((M, K), dtype)
+            t.copy_(parts[rank])
+            comm.all_reduce_(t)
+            want_q, want_s, want_res, _ = add_rmsnorm_quantize_int8(
+                t, weight, 1e-6, None if residual is None else residual.cuda())
+            want_q, want_s = want_q.clone(), want_s.clone()
+            # fused route
+            t2 = comm.buffer((M, K), dtype)
+            t2.copy_(parts[rank])
+            res_shard = None if residual is None else residual[rank * rows:(rank + 1) * rows].contiguous().cuda()
+            xq, a_s, new_res, _ = comm.reduce_rmsnorm_quant(t2, weight, 1e-6, res_shard)
+            torch.cuda.synchronize()
+            same = torch.equal(xq, want_q) and torch.equal(a_s, want_s)
+            if with_res:
+                same = same and torch.equal(new_res.view(torch.int16),
+                                            want_res[rank * rows:(rank + 1) * rows].view(torch.int16))
+            ok = ok and same
+            if not same:
+                notes.append(f"exchange call {call} (M={M} K={K}): differs from all-reduce + norm + quant")
+        ok = ok and _lib.lib().b200q_device_status() == 0
+        # timing at the benchmark's size: fused exchange vs all-reduce + add-RMSNorm + quant
+        M, K = 8192, 1024
+        bufs = [comm.buffer((M, K), torch.bfloat16) for _ in range(2)]
+        for b in bufs:
+            b.normal_()
+        w = torch.ones(K, dtype=torch.bfloat16, device="cuda")
+        res = torch.zeros(M // world, K, dtype=torch.bfloat16, device="cuda")
+        res_full = torch.zeros(M, K, dtype=torch.bfloat16, device="cuda")
+        turn = [0]
+
+        def fused():
+            turn[0] ^= 1
+            comm.reduce_rmsnorm_quant(bufs[turn[0]], w, 1e-6, res)
+
+        def two_kernels():
+            turn[0] ^= 1
+            y = comm.large_(bufs[turn[0]])
+            add_rmsnorm_quantize_int8(y, w, 1e-6, res_full)
+
+        for fn, name in ((fused, "fused exchange"), (two_kernels, "all-reduce + add-RMSNorm + quant")):
+            notes.append(f"8192 x 1024 tp={world} {name}: {_graph_time_us(fn, reps=10):.1f} us")
+        ok = ok and _lib.lib().b200q_device_status() == 0
+    except Exception:  # noqa: BLE001
+        import traceback
+        ok = False
+        notes.append(traceback.format_exc())
+    torch.save({"ok": ok, "notes": notes}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _report(tmp_path, world, name):
+    """Asserts every rank's verdict; the ranks' notes (timings, routes taken) are appended to a
+    log in the directory B200Q_TEST_LOG_DIR names, when it is set."""
+    lines = []
+    for r in range(world):
+        res = torch.load(tmp_path / f"r{r}.pt")
+        print(r, res["notes"])
+        lines.append(f"{name} world={world} rank={r} ok={res['ok']}: " + " | ".join(str(n) for n in res["notes"]))
+    out = os.environ.get("B200Q_TEST_LOG_DIR")
+    if out and Path(out).is_dir():
+        with open(Path(out) / f"tp_tests_world{world}.log", "a") as f:
+            f.write("\n".join(lines) + "\n")
+    for r in range(world):
+        res = torch.load(tmp_path / f"r{r}.pt")
+        assert res["ok"], res["notes"]
+
+
+def test_fused_exchange_matches_allreduce_then_norm_quant(tmp_path):
+    world = min(torch.cuda.device_count(), 8)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    mp.spawn(_exchange_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    _report(tmp_path, world, "exchange")
+
+
 def test_fused_row_parallel_prefill_matches_two_kernel_route(tmp_path):
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)
     if world < 2:
         pytest.skip("needs at least two GPUs")
     mp.spawn(_tiled_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    for r in range(world):
-        res = torch.load(tmp_path / f"r{r}.pt")
-        print(r, res["notes"])
-        assert res["ok"], res["notes"]
+    _report(tmp_path, world, "tiled")
 
 
 def test_fused_row_parallel_decode_matches_two_kernel_route(tmp_path):
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)
     if world < 2:
         pytest.skip("needs at least two GPUs")
     mp.spawn(_fused_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    for r in range(world):
-        res = torch.load(tmp_path / f"r{r}.pt")
-        print(r, res["notes"])
-        assert res["ok"], res["notes"]
+    _report(tmp_path, world, "fused_decode")
 
 
 def test_peer_all_reduce_matches_rank_ordered_fp32_sum(tmp_path):
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), 8)
     if world < 2:
         pytest.skip("needs at least two GPUs")
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    for r in range(world):
-        res = torch.load(tmp_path / f"r{r}.pt")
-        print(r, res["notes"])
-        assert res["ok"], res["notes"]
+    _report(tmp_path, world, "allreduce")

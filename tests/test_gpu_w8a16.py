@@ -47,6 +47,24 @@ def test_golden_cases(golden_cases):
             assert m["relative_l2"] <= 1e-2 and m["cosine_similarity"] >= 0.9999, (c["id"], path, m)
 
 
+def test_benchmark_shape_against_reference_vectors(baseline_shape_golden):
+    # single W8A16 linear 256 x 1024 -> 6144: sampled rows of the reference's own
+    # dequantize-then-matmul output (tests/golden/baseline_shapes_golden.npz), every kernel family
+    import numpy as np
+    z = baseline_shape_golden
+    M, K, N = (int(v) for v in z["w8a16_shape"])
+    q, s = O.make_weight(N, K, seed=0)
+    x = O.make_activation(M, K, seed=0, outliers=False)
+    rows = torch.from_numpy(z["w8a16_rows"])
+    want = torch.from_numpy(z["w8a16_y_rows"].view(np.int16).copy()).view(torch.bfloat16)
+    for path in ("simt", "umma", "umma_swap", None):
+        with forced_path(path):
+            y = apply_int8_weight_only_linear(x.cuda(), q.cuda(), s.cuda())
+        m = O.tensor_metrics(want, y[rows.cuda()])
+        assert m["relative_l2"] <= 1e-2 and m["cosine_similarity"] >= 0.9999, (path, m)
+    assert device_status_ok()
+
+
 def test_all_int8_codes_expand_exactly():
     # every int8 value, -128 included, must reach the tensor cores unchanged: with x = identity
     # rows and unit scales the output is the weight matrix itself

@@ -90,6 +90,28 @@ def test_golden_cases(golden_cases):
             assert m["relative_l2"] <= REL_L2_GATE and m["cosine_similarity"] >= COSINE_GATE, (c["id"], path, m)
 
 
+def test_benchmark_decode_shape_against_reference_vectors(baseline_shape_golden):
+    # W8A8, 16 tokens through 1024 -> 4096: the reference's own quantiser output, exact integer
+    # accumulators and dequantize-then-matmul output (tests/golden/baseline_shapes_golden.npz)
+    import numpy as np
+    z = baseline_shape_golden
+    M, K, N = (int(v) for v in z["w8a8_shape"])
+    q, s = O.make_weight(N, K, seed=1)
+    x = O.make_activation(M, K, seed=1)
+    xq, a_s = quantize_activation_int8(x.cuda())
+    assert torch.equal(xq.cpu(), torch.from_numpy(z["w8a8_xq"]))
+    assert torch.equal(a_s.cpu(), torch.from_numpy(z["w8a8_a_s"]))
+    want = torch.from_numpy(z["w8a8_y"].view(np.int16).copy()).view(torch.bfloat16)
+    for path in ("simt", "umma", "umma_swap", "mma", None):
+        with forced_path(path):
+            acc = w8a8_int32_accumulators(xq, q.cuda())
+            y = apply_w8a8_linear(xq, a_s, q.cuda(), s.cuda(), out_dtype=torch.bfloat16)
+        assert torch.equal(acc.cpu(), torch.from_numpy(z["w8a8_acc_i32"])), path
+        m = O.tensor_metrics(want, y)
+        assert m["relative_l2"] <= REL_L2_GATE and m["cosine_similarity"] >= COSINE_GATE, (path, m)
+    assert device_status_ok()
+
+
 def test_quant_then_gemm_matches_reference_chain():
     # activation quantisation on the GPU feeding the GEMM: the whole W8A8QuantMethod.apply chain
     x, xq, a_s, q, s, _ = problem(300, 512, 1024, seed=21)

@@ -110,6 +110,10 @@ SIGNATURES = {
     "b200q_tp_allreduce_small": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int,
                                             _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_int,
                                             _c.c_int, _c.c_void_p]),
+    "b200q_tp_reduce_rmsnorm_quant": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                                 _c.c_void_p, _c.c_float, _c.c_void_p, _c.c_void_p,
+                                                 _c.c_void_p, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                                 _c.c_int, _c.c_void_p]),
     "b200q_w8a8_gemm_noalloc": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                            _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
                                            _c.c_int, _c.c_void_p]),

@@ -1,6 +1,7 @@
-// Device pieces shared by the activation quantiser and its fused producers (RMSNorm, SiLU-mul):
-// 16-bit unpacking, the packed absolute maximum, and the bit-exact int8 conversion of
-// eight values at a time.
+// Device pieces shared by the activation quantiser and its fused producers (RMSNorm, SiLU-mul,
+// the tensor-parallel reduce + RMSNorm): 16-bit unpacking, the packed absolute maximum, the
+// bit-exact int8 conversion of eight values at a time, row-group reductions and the common
+// "quantise the row held in registers" tail.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -112,6 +113,93 @@ __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
   return v;
 }
+
+// ---- pieces of the kernels that form a row in registers (RMSNorm, SiLU-mul, the
+// tensor-parallel reduce + RMSNorm) and quantise it there
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Two 16-bit values times two 16-bit weights, rounded once to 16 bit (what a 16-bit tensor
+// multiply does).
+template <typename T>
+__device__ __forceinline__ uint32_t mul2_16(uint32_t a, uint32_t w);
+template <>
+__device__ __forceinline__ uint32_t mul2_16<__nv_bfloat16>(uint32_t a, uint32_t w) {
+  const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a),
+                                   *reinterpret_cast<const __nv_bfloat162*>(&w));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <>
+__device__ __forceinline__ uint32_t mul2_16<__half>(uint32_t a, uint32_t w) {
+  const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&w));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+// Reduction over the G threads of a row group (warps of a group are neighbours in the CTA).
+template <int G, bool IS_MAX>
+__device__ __forceinline__ float group_reduce(float v, float* red, int g) {
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  if (G > 32) {
+    constexpr int kWarpsPerRow = G / 32;
+    __syncthreads();  // red may still be read from the previous reduction
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float m = red[g * kWarpsPerRow];
+#pragma unroll
+    for (int i = 1; i < kWarpsPerRow; ++i)
+      m = IS_MAX ? fmaxf(m, red[g * kWarpsPerRow + i]) : m + red[g * kWarpsPerRow + i];
+    v = m;
+  }
+  return v;
+}
+
+// Common tail: y (CHUNKS chunks of 8 values per thread) -> optional store, absmax, int8 codes.
+template <typename T, int G, int CHUNKS>
+__device__ __forceinline__ void quantise_row(const uint4 (&y)[CHUNKS], bool active, int row, int t,
+                                             int g, int nchunk, int K, T* __restrict__ y_out,
+                                             int8_t* __restrict__ xq, float* __restrict__ a_scales,
+                                             float* red) {
+  AbsMax2<T> running;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    running.add(y[c].x);
+    running.add(y[c].y);
+    running.add(y[c].z);
+    running.add(y[c].w);
+  }
+  const float amax = group_reduce<G, true>(running.value(), red, g);
+  if (!active) return;
+  const float scale = fmaxf(__fdiv_rn(amax, 127.0f), 1e-8f);
+  const float inv_scale = __frcp_rn(scale);
+  if (t == 0) a_scales[row] = scale;
+  uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<size_t>(row) * K);
+  uint4* ydst = y_out != nullptr ? reinterpret_cast<uint4*>(y_out + static_cast<size_t>(row) * K) : nullptr;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int idx = c * G + t;
+    if (idx < nchunk) {
+      dst[idx] = quant8<T>(y[c], scale, inv_scale);
+      if (ydst != nullptr) ydst[idx] = y[c];
+    }
+  }
+}
+
 
 }  // namespace
 }  // namespace b200q

@@ -79,6 +79,7 @@ struct PairParams {
   int tiles_m2;   // ceil(M / 256): row tiles of the pair
   int tiles_n;    // ceil(N / 256)
   int k_blocks;
+  int m_fastest;  // order of the tile walk: 1 = neighbouring items share the weight tile
   const float* a_scales;  // per token (W8A8)
   const float* w_scales;  // per channel
   const void* bias;       // per channel, OutT, or nullptr
@@ -112,6 +113,24 @@ __device__ __forceinline__ int row_tile_of(int i, int tiles_m2, const ScatterPar
   const int per_owner = tiles_m2 / sp.world;
   const int owner = (i + sp.rank) % sp.world;
   return owner * per_owner + i / sp.world;
+}
+
+// Tile walk.  The CTA pairs work on about 74 consecutive items at a time, so the operand that
+// changes slowest along the walk is re-read from L2 by neighbouring pairs while the other one
+// streams.  Column tiles fastest (neighbours share token rows and write one row band) unless
+// the weights are the larger operand: then row tiles go fastest, so that each weight tile is
+// fetched from HBM once instead of once per 256-row band (4096 -> 24576 at 8192 tokens, 16-bit
+// weights of 201 MB against a 126 MB L2: 1554 us before, against 1208 us for the library GEMM).
+template <bool SCATTER>
+__device__ __forceinline__ void item_to_tile(int item, const PairParams& pp, const ScatterParams& sp,
+                                             int* tile_n, int* tile_m2) {
+  if (!SCATTER && pp.m_fastest) {
+    *tile_n = item / pp.tiles_m2;
+    *tile_m2 = item - *tile_n * pp.tiles_m2;
+  } else {
+    *tile_n = item % pp.tiles_n;
+    *tile_m2 = row_tile_of<SCATTER>(item / pp.tiles_n, pp.tiles_m2, sp);
+  }
 }
 
 template <typename T>
@@ -280,7 +299,8 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // Weights do not depend on the previous kernel: ask L2 for this CTA's first weight rows while
   // that kernel is still running (a prefetch is only a hint, so it is safe even if they did).
   if (KIND != KIND_F16 && threadIdx.x == 0 && aligned && pair < total_items) {
-    const int row_b = (pair % pp.tiles_n) * kPairBN + static_cast<int>(rank) * kTileRows;
+    const int first_n = pp.m_fastest ? pair / pp.tiles_m2 : pair % pp.tiles_n;
+    const int row_b = first_n * kPairBN + static_cast<int>(rank) * kTileRows;
     const int n = pp.k_blocks < 8 ? pp.k_blocks : 8;
     for (int kb = 0; kb < n; ++kb) ptx::tma_prefetch_l2_2d(&tmap_b, kb * kBlockBytes, row_b);
   }
@@ -297,8 +317,8 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       bool ok = true;
       for (int item = pair; ok && item < total_items; item += num_pairs) {
-        const int tile_n = item % pp.tiles_n;  // column tiles fastest: neighbours write one row band
-        const int tile_m2 = row_tile_of<SCATTER>(item / pp.tiles_n, pp.tiles_m2, sp);
+        int tile_n, tile_m2;
+        item_to_tile<SCATTER>(item, pp, sp, &tile_n, &tile_m2);
         const int row_a = (tile_m2 * 2 + static_cast<int>(rank)) * kTileRows;
         const int row_b = tile_n * kPairBN + static_cast<int>(rank) * kTileRows;
         for (int kb = 0; kb < pp.k_blocks; ++kb) {
@@ -375,8 +395,8 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const OutT* bias = reinterpret_cast<const OutT*>(pp.bias);
     int it = 0;
     for (int item = pair; item < total_items; item += num_pairs, ++it) {
-      const int tile_n = item % pp.tiles_n;
-      const int tile_m2 = row_tile_of<SCATTER>(item / pp.tiles_n, pp.tiles_m2, sp);
+      int tile_n, tile_m2;
+      item_to_tile<SCATTER>(item, pp, sp, &tile_n, &tile_m2);
       const int tile_m = tile_m2 * 2 + static_cast<int>(rank);
       const int buf = it & 1;
       const uint32_t tphase = static_cast<uint32_t>(it >> 1) & 1u;
@@ -554,6 +574,7 @@ PairParams make_params(const GemmArgs& a, int k_bytes) {
   pp.out = a.y;
   pp.status = a.status;
   pp.debug_flags = debug_knob(B200Q_KNOB_FLAGS, 0);
+  pp.m_fastest = a.N > a.M ? 1 : 0;
   return pp;
 }
 

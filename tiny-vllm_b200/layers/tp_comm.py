@@ -40,11 +40,20 @@ class PeerAllReduce:
     """Owns one symmetric data buffer and one symmetric flag pad for a process group."""
 
     def __init__(self, max_bytes: int, group=None, slots: int = 2, fused_bytes: int = 16 << 20,
-                 tiled_prefill: bool = False):
+                 tiled_prefill: bool = False, code_bytes: int | None = None):
+        """``max_bytes``: largest tensor a data slot holds.  ``slots``: number of rotating data
+        slots, AT LEAST 2: the pull all-reduce (two ranks) leaves its input slot readable by
+        the peer until the next collective, so the next partial result must go to another
+        slot.  ``code_bytes``: size of each of the two int8 code buffers that
+        :meth:`reduce_rmsnorm_quant` gathers into (default: ``max_bytes // 2``, i.e. the same
+        number of elements as a 16-bit data slot)."""
         import torch.distributed._symmetric_memory as symm_mem
 
         if not dist.is_initialized():
             raise RuntimeError("PeerAllReduce needs an initialised process group")
+        if slots < 2:
+            raise ValueError("PeerAllReduce needs at least 2 data slots: with one, a rank would "
+                             "overwrite a partial result its peer may still be reading")
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
@@ -81,8 +90,16 @@ class PeerAllReduce:
         if self.tiled_prefill:
             self._stage = symm_mem.empty(self.slot_bytes, dtype=torch.uint8, device=dev)
             self._stage_hdl = symm_mem.rendezvous(self._stage, name)
+        # int8 codes + fp32 scales of the fused reduce + RMSNorm + quantise exchange: two
+        # rotating buffers, each [codes | scales]
+        self.code_bytes = ((code_bytes if code_bytes is not None else max_bytes // 2) + 255) // 256 * 256
+        self._scale_bytes = (self.code_bytes // 16 * 4 + 255) // 256 * 256     # rows are >= 16 wide
+        self._codes = symm_mem.empty(2 * (self.code_bytes + self._scale_bytes), dtype=torch.uint8, device=dev)
+        self._codes_hdl = symm_mem.rendezvous(self._codes, name)
+        self._code_next = 0
         torch.cuda.synchronize()
         dist.barrier(self.group)           # every pad is zero before anyone signals
+        self._code_ptrs = [int(p) for p in self._codes_hdl.buffer_ptrs]
         self._data_ptrs = [int(p) for p in self._data_hdl.buffer_ptrs]
         # multicast mapping of the data buffer (0 when the fabric offers none): in-switch sums
         self._mc_ptr = int(getattr(self._data_hdl, "multicast_ptr", 0) or 0)
@@ -165,6 +182,49 @@ class PeerAllReduce:
                                                     torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "b200q_tp_allreduce_multimem", f"n={t.numel()} world={self.world}")
         return t
+
+    def reduce_rmsnorm_quant(self, partial: torch.Tensor, weight: torch.Tensor, eps: float,
+                             residual: torch.Tensor | None = None, return_normed: bool = False):
+        """The exchange after a row-parallel layer fused with the residual add, RMSNorm and int8
+        quantisation that follow it (``b200q_tp_reduce_rmsnorm_quant``).
+
+        ``partial``: this rank's partial output ``[M, K]`` from :meth:`buffer` (same slot on
+        every rank), ``M`` a multiple of the group size.  ``residual``: THIS RANK'S ROWS of the
+        residual stream, ``[M / world, K]`` (rank ``r`` owns rows ``r * M / world`` onward), or
+        ``None``.  Returns ``(x_q [M, K] int8, a_scales [M] fp32, new_residual [M / world, K] or
+        None, normed [M / world, K] or None)``: codes and scales of ALL rows (gathered from every
+        rank; they live in a symmetric buffer that is reused two calls later), the new residual
+        and, on request, the normalised values of the own rows only."""
+        if not self.owns(partial) or partial.dim() != 2 or partial.dtype not in _DTYPE_IDS:
+            raise RuntimeError("reduce_rmsnorm_quant needs a 2-D fp16/bf16 tensor obtained from buffer()")
+        M, K = partial.shape
+        if M % self.world != 0 or K % 16 != 0:
+            raise RuntimeError("reduce_rmsnorm_quant needs M % world == 0 and K % 16 == 0")
+        if M * K > self.code_bytes or M * 4 > self._scale_bytes:
+            raise RuntimeError(f"[{M}, {K}] codes exceed the symmetric code buffer ({self.code_bytes} bytes)")
+        rows = M // self.world
+        if residual is not None and (tuple(residual.shape) != (rows, K) or residual.dtype != partial.dtype
+                                     or not residual.is_contiguous()):
+            raise RuntimeError(f"residual must be this rank's contiguous [{rows}, {K}] rows in the partial's dtype")
+        if weight.dtype != partial.dtype or weight.numel() != K:
+            raise RuntimeError("weight must have K elements of the partial's dtype")
+        base = self._code_next * (self.code_bytes + self._scale_bytes)
+        self._code_next ^= 1
+        xq = self._codes[base:base + M * K].view(torch.int8).view(M, K)
+        a_s = self._codes[base + self.code_bytes:base + self.code_bytes + 4 * M].view(torch.float32)
+        new_res = torch.empty_like(residual) if residual is not None else None
+        normed = torch.empty((rows, K), dtype=partial.dtype, device=partial.device) if return_normed else None
+        off = partial.data_ptr() - self._data.data_ptr()
+        parts = (ctypes.c_void_p * self.world)(*[p + off for p in self._data_ptrs])
+        xqs = (ctypes.c_void_p * self.world)(*[p + base for p in self._code_ptrs])
+        scs = (ctypes.c_void_p * self.world)(*[p + base + self.code_bytes for p in self._code_ptrs])
+        rc = _lib.lib().b200q_tp_reduce_rmsnorm_quant(
+            parts, self._pad_arr, None if residual is None else residual.data_ptr(),
+            None if new_res is None else new_res.data_ptr(), weight.contiguous().data_ptr(), float(eps),
+            xqs, scs, None if normed is None else normed.data_ptr(), M, K, self.rank, self.world,
+            _DTYPE_IDS[partial.dtype], torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "b200q_tp_reduce_rmsnorm_quant", f"M={M} K={K} world={self.world}")
+        return xq, a_s, new_res, normed
 
     def large_(self, t: torch.Tensor) -> torch.Tensor:
         """All-reduce of a tensor that lives in a symmetric slot by the fastest large-tensor
