@@ -5,7 +5,8 @@ What this recipe does, from the reference checkout where it lies (first argument
 ``oracle/_ref/``, which is git-ignored (it travels with a snapshot of the tree like every
 other built artefact, so a machine without the checkout can still run it):
 
-1. the reference's Python package ``nanovllm/`` is mirrored to ``oracle/_ref/nanovllm/`` so
+1. the reference's Python package ``nanovllm/`` (and its artifact tool ``scripts/quantize.py``)
+   is mirrored to ``oracle/_ref/nanovllm/`` (``oracle/_ref/scripts/``) so
    that its own functions — ``quantize_int8_per_row_dynamic``, ``w8a8_linear_fallback``,
    ``int8_weight_only_linear_fallback``, ``apply_w8a8_linear``,
    ``apply_int8_weight_only_linear`` — can be imported unmodified;
@@ -51,6 +52,9 @@ def build(where: str | None = None, force: bool = False, verbose: bool = False) 
     REF_DIR.mkdir(exist_ok=True)
     shutil.copytree(src / "nanovllm", pkg, dirs_exist_ok=True,
                     ignore=shutil.ignore_patterns("__pycache__", "*.pyc"))
+    if (src / "scripts" / "quantize.py").is_file():   # the reference's offline artifact tool
+        (REF_DIR / "scripts").mkdir(exist_ok=True)
+        shutil.copyfile(src / "scripts" / "quantize.py", REF_DIR / "scripts" / "quantize.py")
     for path in [pkg, *pkg.rglob("*")]:          # the checkout may be read-only; the mirror is not
         path.chmod(path.stat().st_mode | 0o200)
     from torch.utils.cpp_extension import load

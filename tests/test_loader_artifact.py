@@ -148,3 +148,91 @@ def test_loader_errors(tmp_path, tp):
     save_file(art, bad / "model.safetensors")
     with pytest.raises(RuntimeError, match="Missing INT8 quantized tensors"):
         load_model(Toy("int8"), str(bad), "int8")
+
+
+@pytest.mark.parametrize("size", [1, 2, 4, 8])
+@pytest.mark.parametrize("mode", [None, "int8", "w8a8"])
+def test_sharded_reads_equal_whole_tensor_loads(tmp_path, tp, size, mode):
+    # every rank of every group size: parameters filled from slices of the stored tensors equal
+    # those filled by the reference-style weight_loader hooks, and only this rank's share of the
+    # column- / row-split matrices is read
+    src = tmp_path / "hf"
+    src.mkdir()
+    tensors = hf_tensors()
+    if size > 2:        # the toy model has 2 KV heads: give it 8 so that they split 8 ways
+        g = torch.Generator().manual_seed(5)
+        for i in range(2):
+            for n in "kv":
+                tensors[f"layers.{i}.self_attn.{n}_proj.weight"] = torch.randn(8 * HD, HIDDEN, generator=g) * 0.02
+            tensors[f"layers.{i}.self_attn.q_proj.weight"] = torch.randn(8 * HD, HIDDEN, generator=g) * 0.02
+            tensors[f"layers.{i}.self_attn.o_proj.weight"] = torch.randn(HIDDEN, 8 * HD, generator=g) * 0.02
+    save_file(tensors, src / "model.safetensors")
+    path = src
+    if mode is not None:
+        path = tmp_path / "q"
+        QA.quantize_directory(src, path, mode)
+
+    heads, kv_heads = (8, 8) if size > 2 else (NH, NKV)
+
+    class WideAttn(nn.Module):
+        def __init__(self, quant):
+            super().__init__()
+            self.qkv_proj = L.QKVParallelLinear(HIDDEN, HD, heads, kv_heads, quantization=quant)
+            self.o_proj = L.RowParallelLinear(heads * HD, HIDDEN, quantization=quant)
+
+    class WideLayer(nn.Module):
+        def __init__(self, quant):
+            super().__init__()
+            self.self_attn = WideAttn(quant)
+            self.mlp = Mlp(quant)
+            self.input_layernorm = nn.LayerNorm(HIDDEN, bias=False)
+
+    class Wide(Toy):
+        def __init__(self, quant):
+            nn.Module.__init__(self)
+            self.layers = nn.ModuleList(WideLayer(quant) for _ in range(2))
+
+    whole_bytes = None
+    for rank in range(size):
+        tp(rank, size)
+        a, b = Wide(mode), Wide(mode)
+        sa = load_model(a, str(path), mode)                          # sliced reads
+        sb = load_model(b, str(path), mode, sharded_reads=False)     # whole tensors + weight_loader
+        for (na, pa), (nb, pb) in zip(a.named_parameters(), b.named_parameters()):
+            assert na == nb and torch.equal(pa.data, pb.data), (rank, na)
+        whole_bytes = sb["bytes_read"]
+        assert sa["bytes_read"] <= sb["bytes_read"]
+        if size > 1:
+            # the split matrices dominate the toy checkpoint: close to 1 / size of the bytes
+            assert sa["bytes_read"] < sb["bytes_read"] * (1.0 / size + 0.15), (sa, sb)
+    assert whole_bytes > 0
+
+
+def test_streaming_artifact_writes_shards_and_matches_in_memory_builder(tmp_path, tp):
+    tp(0, 1)
+    src = tmp_path / "hf"
+    src.mkdir()
+    tensors = hf_tensors()
+    # source split over two shard files, members of one packed projection in different files
+    names = sorted(tensors)
+    save_file({n: tensors[n] for n in names[::2]}, src / "model-00001-of-00002.safetensors")
+    save_file({n: tensors[n] for n in names[1::2]}, src / "model-00002-of-00002.safetensors")
+    out = tmp_path / "q"
+    files = QA.quantize_directory(src, out, "w8a8", shard_bytes=4096)   # tiny shards: several files
+    assert len(files) > 1 and all(f.name.startswith("model-") for f in files)
+    merged = {}
+    for f in files:
+        part = load_file(f)
+        assert not set(part) & set(merged)
+        merged.update(part)
+    want = QA.build_quantized_tensors(tensors, "w8a8")
+    assert set(merged) == set(want)
+    for k in want:
+        assert torch.equal(merged[k], want[k]), k
+    model = Toy("w8a8")
+    load_model(model, str(out), "w8a8")                                 # the loader reads every shard
+    assert torch.equal(model.layers[1].mlp.down_proj.qweight.data, want["layers.1.mlp.down_proj.qweight"])
+    # duplicate names across source shards are refused
+    save_file({names[0]: tensors[names[0]]}, src / "model-00003-of-00003.safetensors")
+    with pytest.raises(ValueError, match="Duplicate tensor name"):
+        QA.quantize_directory(src, tmp_path / "q2", "w8a8")

@@ -21,6 +21,13 @@ Sharding rules (reference lines in parentheses):
 
 Every layout is described once as a list of ``(dst_offset, dst_size, src_offset,
 src_size)`` segments and copied by one helper.
+
+Besides the reference's ``weight_loader`` hooks (which take the whole stored tensor and keep
+this rank's part), every parameter carries a ``shard_plan(stored_shape, *shard_id)`` hook that
+returns the same copy as a list of ``(dst_index, src_index)`` slice tuples.  A loader that can
+read parts of a stored tensor (safetensors ``get_slice``) uses it to read only this rank's
+share from disk: 1 / tp of the bytes instead of all of them on every rank
+(``nanovllm/utils/loader.py:50-64`` reads every full tensor on every rank).
 """
 from __future__ import annotations
 
@@ -65,6 +72,20 @@ def _tp_coordinates() -> tuple[int, int]:
     return 0, 1
 
 
+def _segment_plan(dim: int, ndim: int, segments, rank: int, size: int):
+    """The copies of :func:`_copy_segments` as ``(dst_index, src_index)`` slice tuples."""
+    plan = []
+    for dst_off, dst_size, src_off, src_size in segments:
+        part = src_size // size
+        lo = src_off + rank * part
+        dst = [slice(None)] * ndim
+        src = [slice(None)] * ndim
+        dst[dim] = slice(dst_off, dst_off + dst_size)
+        src[dim] = slice(lo, lo + part)
+        plan.append((tuple(dst), tuple(src)))
+    return plan
+
+
 def _copy_segments(dst: torch.Tensor, src: torch.Tensor, dim: int, segments, rank: int, size: int):
     """For every segment: split ``src[src_off : src_off+src_size]`` into ``size`` equal
     parts along ``dim`` and copy part ``rank`` to ``dst[dst_off : dst_off+dst_size]``."""
@@ -95,17 +116,31 @@ class LinearBase(nn.Module):
         if self.quant_method is None:
             self.weight = nn.Parameter(torch.empty(output_size, input_size))
             self.weight.weight_loader = self.weight_loader
+            self.weight.shard_plan = self._plan_for("weight")
         else:
             self.quant_method.create_weights(self, input_size, output_size)
             self.qweight.weight_loader = self.qweight_loader
+            self.qweight.shard_plan = self._plan_for("qweight")
             for name in _SCALE_NAMES:
                 if hasattr(self, name):
                     getattr(self, name).weight_loader = self.scales_loader
+                    getattr(self, name).shard_plan = self._plan_for("scales")
         if bias:
             self.bias = nn.Parameter(torch.empty(output_size))
             self.bias.weight_loader = self.bias_loader
+            self.bias.shard_plan = self._plan_for("bias")
         else:
             self.register_parameter("bias", None)
+
+    def _plan_for(self, kind: str):
+        return lambda stored_shape, *shard_id: self.shard_plan(kind, tuple(stored_shape), *shard_id)
+
+    def shard_plan(self, kind: str, stored_shape: tuple, *shard_id):
+        """What this rank copies out of a stored tensor of ``stored_shape`` into the parameter of
+        ``kind`` ("weight" | "qweight" | "scales" | "bias"): ``[(dst_index, src_index), ...]``.
+        Default: the whole tensor (replicated parameters)."""
+        whole = tuple(slice(None) for _ in stored_shape)
+        return [(whole, whole)]
 
     # -- loader hooks; the defaults copy the stored tensor as is -------------
     def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
@@ -158,6 +193,11 @@ class ColumnParallelLinear(LinearBase):
     def scales_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
         self._load_rank_slice(param, loaded_weight, 0)
 
+    def shard_plan(self, kind: str, stored_shape: tuple, *shard_id):
+        rows = stored_shape[0]
+        return _segment_plan(0, len(stored_shape), [(0, rows // self.tp_size, 0, rows)],
+                             self.tp_rank, self.tp_size)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.apply_linear(x)
 
@@ -197,6 +237,14 @@ class _PackedColumnParallel(ColumnParallelLinear):
 
     def scales_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
         self.packed_scales_loader(param, loaded_weight)
+
+    def shard_plan(self, kind: str, stored_shape: tuple, *shard_id):
+        if shard_id and shard_id[0] is not None:    # one unpacked sub-matrix (HF checkpoint)
+            dst_off, dst_size, _, _ = self._segment_of(shard_id[0])
+            segments = [(dst_off, dst_size, 0, stored_shape[0])]
+        else:                                       # the packed tensor of a quantized artifact
+            segments = self._segments()
+        return _segment_plan(0, len(stored_shape), segments, self.tp_rank, self.tp_size)
 
 
 class MergedColumnParallelLinear(_PackedColumnParallel):
@@ -263,6 +311,12 @@ class RowParallelLinear(LinearBase):
 
     def scales_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
         param.data.copy_(loaded_weight)  # one scale per output channel: replicated
+
+    def shard_plan(self, kind: str, stored_shape: tuple, *shard_id):
+        if kind in ("weight", "qweight"):
+            cols = stored_shape[1]
+            return _segment_plan(1, 2, [(0, cols // self.tp_size, 0, cols)], self.tp_rank, self.tp_size)
+        return super().shard_plan(kind, stored_shape)    # scales and bias are replicated
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         bias = self.bias if self.tp_rank == 0 else None
