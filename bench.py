@@ -781,6 +781,12 @@ def run_shape_sweep(args):
     L = _lib.lib()
     ws = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
     peaks = load_peaks()
+    for item in filter(None, args.sweep_knob.split(",")):
+        name, value = item.split("=")
+        _lib.check(L.b200q_debug_set(getattr(_lib, "KNOB_" + name), int(value)), "debug_set")
+    if args.sweep_force:
+        L.b200q_debug_force_path({"simt": _lib.PATH_SIMT_STREAM, "umma": _lib.PATH_UMMA,
+                                  "umma_swap": _lib.PATH_UMMA_SWAP, "mma": _lib.PATH_MMA_STREAM}[args.sweep_force])
 
     def time_op(op, M, N, K, iters):
         nbuf = max(2, min(16, int(300e6 // max(1, N * K + 2 * M * N)) + 1))
@@ -838,6 +844,10 @@ def run_shape_sweep(args):
 
     results = []
     shapes = [(name, n, k) for name, k, n, _ in PROJECTIONS]
+    if args.sweep_model == "8b":
+        # Qwen3-8B projections, whole and as the shards of 8 tensor-parallel ranks
+        shapes = [(name, n, k) for name, k, n in EIGHT_B] + \
+                 [("qkv_tp8", 768, 4096), ("o_tp8", 4096, 512), ("gate_up_tp8", 3072, 4096), ("down_tp8", 4096, 1536)]
     want_ops = args.sweep_op.split(",") if args.sweep_op else ["w8a8", "w8a16", "act_quant", "fused_quant"]
     want_m = [int(m) for m in args.sweep_m.split(",")] if args.sweep_m else [1, 16, 128, 512, TOKENS]
     for op in ("w8a8", "w8a16"):
@@ -845,7 +855,7 @@ def run_shape_sweep(args):
             continue
         for M in want_m:
             for name, N, K in shapes:
-                us = time_op(op, M, N, K, 20 if M == TOKENS else 100)
+                us = time_op(op, M, N, K, 20 if M >= 2048 or N * K > (32 << 20) else 100)
                 in_bytes = M * K * (1 if op == "w8a8" else 2)
                 alg_bytes = in_bytes + N * K + 4 * N + 2 * M * N + (4 * M if op == "w8a8" else 0)
                 ops = 2.0 * M * N * K
@@ -896,6 +906,11 @@ def main():
                     help="sum row-parallel outputs with NCCL instead of the peer-memory kernel")
     ap.add_argument("--sweep-op", default="", help="shape_sweep: comma list of w8a8,w8a16,act_quant,fused_quant")
     ap.add_argument("--sweep-m", default="", help="shape_sweep: comma list of token counts")
+    ap.add_argument("--sweep-model", default="0.6b", choices=["0.6b", "8b"],
+                    help="shape_sweep: projections of Qwen3-0.6B or of Qwen3-8B (and its TP=8 shards)")
+    ap.add_argument("--sweep-force", default="", choices=["", "simt", "umma", "umma_swap", "mma"],
+                    help="shape_sweep: force one kernel family (a debugging aid; default: the library's choice)")
+    ap.add_argument("--sweep-knob", default="", help="shape_sweep: comma list of debug knobs NAME=VALUE")
     ap.add_argument("--mode", default="headline", choices=["headline", "shape_sweep"],
                     help="shape_sweep prints per-shape kernel times (decode and prefill shapes)")
     args = ap.parse_args()

@@ -214,7 +214,9 @@ enum {
   B200Q_KNOB_NO_PDL = 12,          /* 1: plain stream order instead of programmatic dependent launch */
   B200Q_KNOB_WAIT_CYCLES = 13,     /* limit of one wait on a peer GPU, in SM cycles (default about 2e9) */
   B200Q_KNOB_PAIR_MIN_TILES = 14,  /* CTA-pair kernels: fewest 256 x 256 tiles a problem must have */
-  B200Q_KNOB_COUNT = 16
+  B200Q_KNOB_BULK_DECODE = 15,  /* persistent ring-fed decode kernels: 1 never, 2 wherever they can run */
+  B200Q_KNOB_BULK_SLOTS = 16,   /* ring depth per consumer warp of those kernels (>= 2; default: what fits) */
+  B200Q_KNOB_COUNT = 20
 };
 int b200q_debug_set(int knob, int value);
 void b200q_debug_reset(void);

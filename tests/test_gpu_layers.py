@@ -94,3 +94,55 @@ def test_cuda_graph_capture_of_decode_call(quant, scale, bs):
     torch.cuda.synchronize()
     assert torch.equal(static_y, eager1)
     assert device_status_ok()
+
+
+@pytest.mark.parametrize("quant,scale", [("int8", "scales"), ("w8a8", "w_scales")])
+def test_cuda_graphs_for_the_runner_batch_list_share_one_pool(quant, scale):
+    # The reference's runner captures one decode graph per batch size of
+    # [1, 2, 4, 8] + range(16, max_bs + 1, 16), largest first, all in ONE memory pool, over views of
+    # the same static buffers (nanovllm/engine/model_runner.py:298-335).  The same here over a
+    # decoder layer's four projections (qkv -> o, gate_up -> down): every graph must replay to
+    # what the eager call gives for that batch size, also after the other graphs were replayed.
+    max_bs = 512
+    sizes = [1, 2, 4, 8] + list(range(16, max_bs + 1, 16))
+    hidden, inter = 1024, 3072
+    layers = {
+        "qkv": (build(L.QKVParallelLinear, quant, hidden, 128, 16, 8), 4096, hidden),
+        "o": (build(L.RowParallelLinear, quant, 2048, hidden), hidden, 2048),
+        "gate_up": (build(L.MergedColumnParallelLinear, quant, hidden, [inter, inter]), 2 * inter, hidden),
+        "down": (build(L.RowParallelLinear, quant, inter, hidden), hidden, inter),
+    }
+    for i, (name, (layer, n, k)) in enumerate(layers.items()):
+        q, s = O.make_weight(n, k, seed=20 + i)
+        layer.qweight.data.copy_(q)
+        getattr(layer, scale).data.copy_(s)
+
+    def block(x):
+        qkv = layers["qkv"][0](x)
+        attn = layers["o"][0](qkv[:, :2048].contiguous())
+        gu = layers["gate_up"][0](attn)
+        return layers["down"][0]((gu[:, :inter] * torch.sigmoid(gu[:, inter:])).contiguous())
+
+    static_x = torch.zeros(max_bs, hidden, dtype=torch.bfloat16, device="cuda")
+    static_y = torch.zeros(max_bs, hidden, dtype=torch.bfloat16, device="cuda")
+    probe = O.make_activation(max_bs, hidden, seed=77).cuda()
+    graphs, pool = {}, None
+    for bs in reversed(sizes):
+        static_x[:bs] = probe[:bs]
+        static_y[:bs] = block(static_x[:bs])          # warm-up, as the runner does
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool):
+            static_y[:bs] = block(static_x[:bs])
+        if pool is None:
+            pool = g.pool()
+        graphs[bs] = g
+    torch.cuda.synchronize()
+    other = O.make_activation(max_bs, hidden, seed=78).cuda()
+    for bs in (1, 2, 8, 16, 48, 64, 80, 256, 496, 512, 4, 32):      # out of capture order on purpose
+        static_x[:bs] = other[:bs]
+        graphs[bs].replay()
+        torch.cuda.synchronize()
+        want = block(other[:bs])
+        assert torch.equal(static_y[:bs], want), bs
+    assert len(graphs) == 36
+    assert device_status_ok()

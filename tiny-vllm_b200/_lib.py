@@ -56,6 +56,8 @@ KNOB_W8A16_PAIR_MIN_M = 11
 KNOB_NO_PDL = 12
 KNOB_WAIT_CYCLES = 13
 KNOB_PAIR_MIN_TILES = 14
+KNOB_BULK_DECODE = 15
+KNOB_BULK_SLOTS = 16
 
 # B200Q_VERSION of include/b200q.h this binding was written for
 ABI_VERSION = 2

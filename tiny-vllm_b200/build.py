@@ -22,7 +22,7 @@ LIB_PATH = LIB_DIR / "libb200q.so"
 HEADER = PKG_DIR.parent / "include" / "b200q.h"
 
 SOURCES = ["api.cu", "act_quant.cu", "act_quant_fused.cu", "gemm_simt.cu", "gemm_umma.cu", "gemm_umma_w8a16.cu", "gemm_umma_w8a16_ts.cu",
-           "gemm_umma_pair.cu", "gemm_mma_decode.cu", "tp_allreduce.cu", "tp_reduce_norm_quant.cu"]
+           "gemm_umma_pair.cu", "gemm_mma_decode.cu", "gemm_bulk_decode.cu", "tp_allreduce.cu", "tp_reduce_norm_quant.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -72,9 +72,14 @@ int check_dims(int M, int N, int K) {
 // so its range shrinks as N grows; thresholds from graph-replayed launches of the
 // Qwen3-0.6B projections at M = 32, 48, 64 (e.g. M = 48: 4.6 vs 7.6 us for 2048 -> 1024,
 // 7.3 vs 6.4 us for 1024 -> 6144).
+// Matrices of 8 MB and more (the 8B model): the ring-fed persistent kernels take M <= 32
+// (M <= 16 for the widest projections: 24576 channels at M = 32 run 29.9 us there against
+// 24.1 us on the tcgen05 kernel), the tcgen05 kernels the rest; the register-streaming kernel's
+// activation re-reads, N / 8 x M x K bytes from L2, rule it out (M = 64: 35-101 us against 13-24).
 int auto_path_w8a8(int M, int N, int K) {
-  (void)K;
   if (M <= debug_knob(B200Q_KNOB_SIMT_MAX_M, 0)) return B200Q_PATH_SIMT_STREAM;
+  if (static_cast<long long>(N) * K >= (8ll << 20))
+    return (M <= 16 || (M <= 32 && N < 16384)) ? B200Q_PATH_MMA_STREAM : B200Q_PATH_UMMA;
   if (M <= 32 || (M <= 48 && N <= 4096) || (M <= 64 && N <= 2048)) return B200Q_PATH_MMA_STREAM;
   return B200Q_PATH_UMMA;
 }
@@ -82,9 +87,13 @@ int auto_path_w8a8(int M, int N, int K) {
 // Kernel family for a W8A16 problem when nothing is forced.
 // Same for W8A16, where the tcgen05 kernel's expansion stage costs more at small M
 // (M = 64: 7.2 vs 17.7 us for 2048 -> 1024, 12.4 vs 11.0 us for 1024 -> 6144).
+// Matrices of 8 MB and more: the ring-fed kernel takes one token tile (M <= 16); beyond it the
+// register-streaming kernel re-reads N / 8 x M x 2 K bytes of activations from L2 (M = 32 on
+// 24576 x 4096: 79 us against 52 us for the tcgen05 kernel at M = 64).
 int auto_path_w8a16(int M, int N, int K) {
-  (void)K;
   if (M <= debug_knob(B200Q_KNOB_SIMT_MAX_M, 0)) return B200Q_PATH_SIMT_STREAM;
+  if (static_cast<long long>(N) * K >= (8ll << 20))
+    return M <= 16 ? B200Q_PATH_MMA_STREAM : B200Q_PATH_UMMA;
   if (M <= 48 || (M <= 64 && N <= 4096)) return B200Q_PATH_MMA_STREAM;
   return B200Q_PATH_UMMA;
 }
@@ -111,7 +120,8 @@ int run_w8a8(GemmArgs& a) {
   }
   if (path == B200Q_PATH_MMA_STREAM) {
     if (!mma_decode_applicable(a.M)) return B200Q_ERR_UNSUPPORTED_SHAPE;
-    cudaError_t e = launch_w8a8_mma_decode(a);
+    cudaError_t e = bulk_decode_applicable(a.M, a.N, a.K, false) ? launch_w8a8_bulk_decode(a)
+                                                          : launch_w8a8_mma_decode(a);
     if (e != cudaSuccess) {
       note_cuda_error(e);
       return B200Q_ERR_LAUNCH;
@@ -385,7 +395,8 @@ int b200q_w8a16_gemm(const void* x, const int8_t* qweight, const float* scales, 
   }
   if (path == B200Q_PATH_MMA_STREAM) {
     if (!mma_decode_applicable(M)) return B200Q_ERR_UNSUPPORTED_SHAPE;
-    cudaError_t e = launch_w8a16_mma_decode(a);
+    cudaError_t e = bulk_decode_applicable(M, N, K, true) ? launch_w8a16_bulk_decode(a)
+                                                    : launch_w8a16_mma_decode(a);
     if (e != cudaSuccess) {
       note_cuda_error(e);
       return B200Q_ERR_LAUNCH;
@@ -430,6 +441,8 @@ const char* b200q_select_path(int op, int M, int N, int K) {
     case B200Q_PATH_SIMT_STREAM:
       return a16 ? "simt_stream_w8a16" : "simt_stream_dp4a";
     case B200Q_PATH_MMA_STREAM:
+      if (bulk_decode_applicable(M, N, K, a16))
+        return a16 ? "bulk_ring_w8a16_persistent" : "bulk_ring_s8_persistent";
       return a16 ? "mma_stream_w8a16_splitk" : "mma_stream_s8_splitk";
     case B200Q_PATH_UMMA:
       if (!a16 && umma_pair_applicable(M, N, K, false)) return "umma_i8_pair_tokens256";

@@ -75,6 +75,12 @@ int launch_w8a8_mma_decode_fused(const GemmArgs& a, void* const* peer_recv,
 int launch_w8a16_mma_decode_fused(const GemmArgs& a, void* const* peer_recv,
                                   void* const* peer_flags, size_t recv_bytes, int rank, int world);
 
+// gemm_bulk_decode.cu: persistent decode kernels for large matrices; a producer warp streams
+// weights and activations through a shared-memory ring of bulk asynchronous copies
+bool bulk_decode_applicable(int M, int N, int K, bool a16);
+cudaError_t launch_w8a8_bulk_decode(const GemmArgs& a);
+cudaError_t launch_w8a16_bulk_decode(const GemmArgs& a);
+
 // gemm_umma.cu
 bool umma_make_plan(int op, int M, int N, int K, int swap, UmmaPlan* plan);
 // Returns a B200Q_* code.
