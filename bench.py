@@ -855,7 +855,7 @@ def run_shape_sweep(args):
             continue
         for M in want_m:
             for name, N, K in shapes:
-                us = time_op(op, M, N, K, 20 if M >= 2048 or N * K > (32 << 20) else 100)
+                us = time_op(op, M, N, K, args.sweep_iters or (20 if M >= 2048 or N * K > (32 << 20) else 100))
                 in_bytes = M * K * (1 if op == "w8a8" else 2)
                 alg_bytes = in_bytes + N * K + 4 * N + 2 * M * N + (4 * M if op == "w8a8" else 0)
                 ops = 2.0 * M * N * K
@@ -868,7 +868,7 @@ def run_shape_sweep(args):
     for name, N, K in shapes:
         if "act_quant" not in want_ops:
             break
-        us = time_op("act_quant", TOKENS, N, K, 50)
+        us = time_op("act_quant", TOKENS, N, K, args.sweep_iters or 50)
         b = 3 * TOKENS * K + 4 * TOKENS
         results.append({"op": "act_quant", "proj": name, "M": TOKENS, "K": K, "us": round(us, 2),
                         "algorithmic_gbs": round(b / us / 1e3, 1),
@@ -877,7 +877,7 @@ def run_shape_sweep(args):
         # quantisation fused into its producers: hidden-size rows (norm) and intermediate-size
         # rows (activation) of Qwen3-0.6B at the prefill token count
         for op, K, per_row in (("add_rmsnorm_quant", 1024, 7 * 1024 + 4), ("silu_mul_quant", 3072, 5 * 3072 + 4)):
-            us = time_op(op, TOKENS, 8, K, 50)
+            us = time_op(op, TOKENS, 8, K, args.sweep_iters or 50)
             b = per_row * TOKENS
             results.append({"op": op, "M": TOKENS, "K": K, "us": round(us, 2),
                             "algorithmic_gbs": round(b / us / 1e3, 1),
@@ -908,6 +908,8 @@ def main():
     ap.add_argument("--sweep-m", default="", help="shape_sweep: comma list of token counts")
     ap.add_argument("--sweep-model", default="0.6b", choices=["0.6b", "8b"],
                     help="shape_sweep: projections of Qwen3-0.6B or of Qwen3-8B (and its TP=8 shards)")
+    ap.add_argument("--sweep-iters", type=int, default=0,
+                    help="shape_sweep: launches per graph (default 20 or 100 by size); 1 keeps a profiler capture short")
     ap.add_argument("--sweep-force", default="", choices=["", "simt", "umma", "umma_swap", "mma"],
                     help="shape_sweep: force one kernel family (a debugging aid; default: the library's choice)")
     ap.add_argument("--sweep-knob", default="", help="shape_sweep: comma list of debug knobs NAME=VALUE")

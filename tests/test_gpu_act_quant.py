@@ -52,7 +52,7 @@ def test_strided_rows_and_empty():
 
 
 def test_full_size_properties():
-    # BASELINE sweep size: codes bounded, scale * 127 reproduces the row maximum, idempotent
+    # the benchmark's prefill size (8192 tokens, widest input): codes bounded, scale * 127 reproduces the row maximum, idempotent
     x = O.make_activation(8192, 3072, seed=11).cuda()
     xq, a_s = quantize_activation_int8(x)
     assert int(xq.abs().max()) == 127 and int(xq.min()) >= -127

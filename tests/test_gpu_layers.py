@@ -146,3 +146,22 @@ def test_cuda_graphs_for_the_runner_batch_list_share_one_pool(quant, scale):
         assert torch.equal(static_y[:bs], want), bs
     assert len(graphs) == 36
     assert device_status_ok()
+
+
+def test_apply_quantized_writes_into_a_caller_buffer():
+    # the row-parallel partial of a tensor-parallel exchange is produced straight into the
+    # symmetric buffer: same bits as a fresh output, and the given tensor is the one returned
+    layer = build(L.RowParallelLinear, "w8a8", 2048, 1024)
+    q, s = O.make_weight(1024, 2048, seed=9)
+    layer.qweight.weight_loader(layer.qweight, q)
+    layer.w_scales.weight_loader(layer.w_scales, s)
+    x = O.make_activation(64, 2048, seed=2).cuda()
+    x_q, a_s = layer.quant_method.quantize_activation(x)
+    fresh = layer.quant_method.apply_quantized(x_q, a_s, layer, torch.bfloat16)
+    slab = torch.zeros(3, 64, 1024, dtype=torch.bfloat16, device="cuda")
+    got = layer.quant_method.apply_quantized(x_q, a_s, layer, torch.bfloat16, out=slab[1])
+    assert got.data_ptr() == slab[1].data_ptr()
+    assert torch.equal(slab[1], fresh) and not slab[0].any() and not slab[2].any()
+    with pytest.raises(RuntimeError):
+        layer.quant_method.apply_quantized(x_q, a_s, layer, torch.bfloat16, out=slab[1].t())
+    assert device_status_ok()

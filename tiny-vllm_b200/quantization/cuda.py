@@ -245,9 +245,12 @@ def apply_w8a8_linear(
     bias: torch.Tensor | None = None,
     out_dtype: torch.dtype = torch.float16,
     out_shape: tuple[int, ...] | None = None,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """W8A8 linear: exact int32 ``x_q @ qweight.T``, then
-    ``(acc * a_scales[:, None]) * w_scales[None, :] + bias`` cast to ``out_dtype``."""
+    ``(acc * a_scales[:, None]) * w_scales[None, :] + bias`` cast to ``out_dtype``.
+    ``out``: a contiguous ``[M, N]`` tensor of ``out_dtype`` to write into instead of a new one
+    (e.g. a slot of the symmetric buffer that a tensor-parallel exchange reads)."""
     _check_w8a8(x_q, a_scales, qweight, w_scales, bias, out_dtype)
     x_q = x_q.contiguous()
     a_scales = a_scales.contiguous()
@@ -256,7 +259,13 @@ def apply_w8a8_linear(
     bias = None if bias is None else bias.contiguous()
     M, K = x_q.shape
     N = qweight.shape[0]
-    y = torch.empty((M, N), dtype=out_dtype, device=x_q.device)
+    if out is None:
+        y = torch.empty((M, N), dtype=out_dtype, device=x_q.device)
+    else:
+        if tuple(out.shape) != (M, N) or out.dtype != out_dtype or not out.is_contiguous() \
+                or out.device != x_q.device:
+            raise RuntimeError(f"out must be a contiguous [{M}, {N}] {out_dtype} tensor on {x_q.device}")
+        y = out
     L = _lib.lib()
     with torch.cuda.device(x_q.device):
         ws_bytes = L.b200q_workspace_bytes(_lib.OP_W8A8, M, N, K)

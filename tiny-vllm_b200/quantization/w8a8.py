@@ -37,14 +37,17 @@ class W8A8QuantMethod(QuantMethod):
 
     def apply_quantized(self, x_q: torch.Tensor, a_scales: torch.Tensor, layer: nn.Module,
                         out_dtype: torch.dtype, bias: torch.Tensor | None = None,
-                        out_shape: tuple[int, ...] | None = None) -> torch.Tensor:
+                        out_shape: tuple[int, ...] | None = None,
+                        out: torch.Tensor | None = None) -> torch.Tensor:
         """The linear on activations that are already quantised — by
         ``add_rmsnorm_quantize_int8`` / ``silu_mul_quantize_int8`` fused into the producer of
         ``x``, or by ``quantize_activation``.  (No counterpart in the reference, whose ``apply``
-        always quantises itself: ``nanovllm/quantization/w8a8.py:25-40``.)"""
+        always quantises itself: ``nanovllm/quantization/w8a8.py:25-40``.)  ``out``: a
+        contiguous ``[tokens, out_features]`` tensor to write into, e.g. ``comm.buffer(...)`` of
+        the tensor-parallel communicator when ``comm.reduce_rmsnorm_quant`` consumes the result."""
         return apply_w8a8_linear(x_q, a_scales, layer.qweight, layer.w_scales,
                                  bias=layer.bias if bias is None else bias,
-                                 out_dtype=out_dtype, out_shape=out_shape)
+                                 out_dtype=out_dtype, out_shape=out_shape, out=out)
 
     def apply_row_parallel(self, x: torch.Tensor, layer: nn.Module, bias, comm):
         """Quantise, multiply and sum over the tensor-parallel ranks with the exchange fused
