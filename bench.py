@@ -8,14 +8,20 @@ epilogue (bf16 out).  Inputs are seeded synthetic tensors (N(0,1) activations wi
 1 % outlier channels x20, N(0,0.02) weights quantised per channel).
 
 With --gpus N > 1 (launched by torchrun, one rank per GPU) the same 8192 tokens run
-tensor-parallel: qkv / gate_up split their output channels, o / down split their input
-features and are followed by an NCCL all-reduce of the bf16 result ("strong" scaling).
+tensor-parallel ("strong" scaling): qkv / gate_up split their output channels, o / down split
+their input features, and what follows a row-parallel layer in the model — sum over ranks,
+residual add, RMSNorm, quantisation for the next projection — is one fused exchange kernel
+over peer memory whose int8 codes feed the next GEMM (``--tp-step allreduce``: plain
+all-reduce and a stand-alone quantiser in front of every GEMM instead).  Every N > 1 run checks
+the exchange bit for bit against all-gather + rank-ordered sum (``exchange_check``).
 
 Prints ONE JSON line (rank 0).  ``value`` is device-timed with inputs resident in HBM;
 ``e2e`` goes through the layer API with host buffers (H2D of activations, D2H of
 outputs inside the timed region); ``roofline`` is for the GEMM kernel, from CUDA-event
-durations of its launches inside the timed region; ``cpu_baseline`` times the CPU
-oracle's dequantize-then-matmul path on the host cores.
+durations of graphs of back-to-back launches taken right after the timed region;
+``cpu_baseline`` times the reference's CPU path (or the oracle's port of it) on the host cores;
+``detail`` holds the other kernels of the path on the same shapes (W8A16, the library bf16
+GEMM, decode batches, the Qwen3-8B shapes, the reference's own CUDA kernels).
 
 ``--impl reference`` times the reference's own CPU implementation of the path — its
 ``quantize_int8_per_row_dynamic`` and ``w8a8_linear_fallback`` from the mirror that
