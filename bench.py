@@ -764,6 +764,13 @@ def run_gpu_arm(args):
         }
         if exchange_check is not None:
             line["exchange_check"] = exchange_check
+        rg = detail.get("reference_gpu", {})
+        if "step_tops" in rg:
+            # the reference's own CUDA kernels on this GPU, same step (vs_baseline stays null:
+            # the reference publishes no number for this metric)
+            line["vs_reference_gpu"] = {"ratio": value / rg["step_tops"], "reference_step_tops": rg["step_tops"],
+                                        "what": "this step's TOPS / the same step through the reference's "
+                                                "quantiser + WMMA kernel on the same B200 (detail.reference_gpu)"}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line))

@@ -374,6 +374,7 @@ def _tiled_worker(rank, world, port, out_dir):
                                                 (torch.bfloat16, 4096, 1000, 1024, False),
                                                 (torch.bfloat16, 1024, 1024, 512, False)):
             K = K_local * world
+            M = -(-M // (world * 256)) * (world * 256)   # the route takes whole 256-row tiles per rank
             q, s = O.make_weight(N, K, seed=41)
             prev = torch.get_default_dtype()
             torch.set_default_dtype(dtype)
