@@ -209,12 +209,13 @@ template <>
 __device__ __forceinline__ uint2 expand4<__nv_bfloat16>(uint32_t w) {
   // 0x4B000000 | u is the float 2^23 + u; subtract 2^23 + 128; at most 8 significant bits
   const uint32_t t = w ^ 0x80808080u;
-  const float m = -8388736.f;
-  const float f0 = __fadd_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7540)), m);
-  const float f1 = __fadd_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7541)), m);
-  const float f2 = __fadd_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7542)), m);
-  const float f3 = __fadd_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7543)), m);
-  const __nv_bfloat162 a = __floats2bfloat162_rn(f0, f1), b = __floats2bfloat162_rn(f2, f3);
+  // packed fp32 adds (each half rounds like the scalar instruction; the sums are exact anyway)
+  const float2 m = make_float2(-8388736.f, -8388736.f);
+  const float2 f01 = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7540)),
+                                            __uint_as_float(__byte_perm(t, 0x4B000000u, 0x7541))), m);
+  const float2 f23 = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7542)),
+                                            __uint_as_float(__byte_perm(t, 0x4B000000u, 0x7543))), m);
+  const __nv_bfloat162 a = __floats2bfloat162_rn(f01.x, f01.y), b = __floats2bfloat162_rn(f23.x, f23.y);
   return make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
 }
 
