@@ -216,6 +216,7 @@ enum {
   B200Q_KNOB_PAIR_MIN_TILES = 14,  /* CTA-pair kernels: fewest 256 x 256 tiles a problem must have */
   B200Q_KNOB_BULK_DECODE = 15,  /* persistent ring-fed decode kernels: 1 never, 2 wherever they can run */
   B200Q_KNOB_BULK_SLOTS = 16,   /* ring depth per consumer warp of those kernels (>= 2; default: what fits) */
+  B200Q_KNOB_BULK_WPP = 17,     /* consumer warps per ring of the W8A8 one-token-tile kernel: 1 or 2 (default 2) */
   B200Q_KNOB_COUNT = 20
 };
 int b200q_debug_set(int knob, int value);

@@ -56,6 +56,8 @@ def test_w8a8_bit_exact(M, N, K, oracle_c_lib):
         assert select_path(_lib.OP_W8A8, M, N, K).startswith("mma_stream")
         y_regs = apply_w8a8_linear(*dev, bias=b.cuda(), out_dtype=torch.bfloat16)
     assert torch.equal(bits(y), bits(y_regs))
+    with forced_path("mma"), knobs(BULK_DECODE=2, BULK_WPP=1):   # one consumer warp per ring
+        assert torch.equal(bits(apply_w8a8_linear(*dev, bias=b.cuda(), out_dtype=torch.bfloat16)), bits(y))
     assert torch.equal(acc.cpu(), ref_acc)
     assert torch.equal(bits(y.cpu()), bits(O.w8a8_native_epilogue(ref_acc, a_s, s, b, torch.bfloat16)))
     assert device_status_ok()

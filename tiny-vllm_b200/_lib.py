@@ -58,6 +58,7 @@ KNOB_WAIT_CYCLES = 13
 KNOB_PAIR_MIN_TILES = 14
 KNOB_BULK_DECODE = 15
 KNOB_BULK_SLOTS = 16
+KNOB_BULK_WPP = 17
 
 # B200Q_VERSION of include/b200q.h this binding was written for
 ABI_VERSION = 2

@@ -21,8 +21,8 @@
 //     of 0.5-1 KB were tried first: they retire at about one copy per 80 cycles per SM whatever
 //     their size, 6-12 bytes per cycle, half of what the register kernel reaches.)
 //
-// Work split: K is cut into segments of 128 elements; segment s belongs to consumer warp
-// s % 8.  Within a segment lane (g = lane / 4, t = lane % 4) owns elements [32 t, 32 t + 32) of
+// Work split: K is cut into segments of 128 elements; segment s belongs to ring s % 8, which
+// one consumer warp reads (or two, each taking half of the tile's rows).  Within a segment lane (g = lane / 4, t = lane % 4) owns elements [32 t, 32 t + 32) of
 // weight rows g, g + 8, ..., g + 40 of the unit and of token rows g, g + 8 of every 16-token
 // tile.  Which physical k sits in which MMA slot does not matter as long as both operands agree:
 // 16-byte piece q of row r lies at r * 128 + ((q ^ (r & 7)) << 4) under the swizzle, and with
@@ -48,16 +48,16 @@
 namespace b200q {
 namespace {
 
-constexpr int kConsumerWarps = 8;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;  // + the producer warp
+constexpr int kPipes = 8;                        // rings per CTA = producer lanes
+// A kernel has kPipes * WPP consumer warps (WPP = warps per ring: 1, or 2 sharing every tile,
+// each taking half of its rows) and one producer warp.
 constexpr int kSeg = 128;                        // K elements of one segment (one slot)
 constexpr int kUnitRows = 48;                    // channels per unit of work (6 MMA n-tiles)
 constexpr int kNT = kUnitRows / 8;
 constexpr int kMaxSlots = 8;                     // ring depth per consumer warp
 constexpr int kMaxMT = 2;  // token tiles: more would not fit the register file beside the prefetch
-constexpr int kRedBytes = kConsumerWarps * 16 * kUnitRows * 4;
-constexpr int kBarBytes = 2 * kConsumerWarps * kMaxSlots * 8;
+constexpr int kRedBytes = kPipes * 16 * kUnitRows * 4;
+constexpr int kBarBytes = 2 * kPipes * kMaxSlots * 8;
 constexpr int kSmemLimit = 227 * 1024;
 
 template <typename T>
@@ -169,8 +169,9 @@ __host__ __device__ __forceinline__ void unit_range(const Share& s, int u, int& 
   rows = s.lo + n * (u + 1) / s.units - ulo;
 }
 
+template <int THREADS>
 __device__ __forceinline__ void consumer_barrier() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
 }
 
 // Producer lane `pipe` (0-7) feeds consumer warp `pipe`: segments pipe, pipe + 8, ... of every
@@ -179,7 +180,7 @@ __device__ __forceinline__ void consumer_barrier() {
 __device__ __forceinline__ void produce(const CUtensorMap* tm_w, const StreamPlan& p, const Share& sh,
                                         int pipe, uint32_t ring, uint64_t* full, uint64_t* empty,
                                         volatile int* abort_flag) {
-  const int my_segs = (p.segs - pipe + kConsumerWarps - 1) / kConsumerWarps;
+  const int my_segs = (p.segs - pipe + kPipes - 1) / kPipes;
   const int total = sh.units * my_segs;
   int it = 0;
   for (; it < total; ++it) {
@@ -189,7 +190,7 @@ __device__ __forceinline__ void produce(const CUtensorMap* tm_w, const StreamPla
       break;
     int ulo, rows;
     unit_range(sh, it / my_segs, ulo, rows);
-    const int k0 = (pipe + kConsumerWarps * (it % my_segs)) * kSeg;
+    const int k0 = (pipe + kPipes * (it % my_segs)) * kSeg;
     const uint32_t bar = ptx::smem_u32(full + slot);
     ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(p.tx_bytes));
     ptx::tma_load_2d(ring + slot * p.slot_bytes, tm_w, bar, k0, ulo);
@@ -217,15 +218,16 @@ __device__ __forceinline__ CtaSmem carve(uint8_t* raw, const StreamPlan& p) {
   CtaSmem c;
   const uint32_t a = ptx::smem_u32(raw);
   c.base = raw + ((1024u - (a & 1023u)) & 1023u);
-  c.red = c.base + kConsumerWarps * p.slots * p.slot_bytes;
+  c.red = c.base + kPipes * p.slots * p.slot_bytes;
   c.full = reinterpret_cast<uint64_t*>(c.red + kRedBytes);
-  c.empty = c.full + kConsumerWarps * kMaxSlots;
-  c.abort_flag = reinterpret_cast<volatile int*>(c.empty + kConsumerWarps * kMaxSlots);
+  c.empty = c.full + kPipes * kMaxSlots;
+  c.abort_flag = reinterpret_cast<volatile int*>(c.empty + kPipes * kMaxSlots);
   return c;
 }
-__device__ __forceinline__ void init_barriers(const CtaSmem& c, const StreamPlan& p) {
-  if (threadIdx.x < 2 * kConsumerWarps * kMaxSlots) {  // full and empty barriers are adjacent
-    ptx::mbar_init(ptx::smem_u32(c.full + threadIdx.x), 1);
+__device__ __forceinline__ void init_barriers(const CtaSmem& c, const StreamPlan& p, int wpp) {
+  if (threadIdx.x < 2 * kPipes * kMaxSlots) {  // full and empty barriers are adjacent
+    // a tile is filled by one TMA load and released by the wpp warps that read it
+    ptx::mbar_init(ptx::smem_u32(c.full + threadIdx.x), threadIdx.x < kPipes * kMaxSlots ? 1 : wpp);
     if (threadIdx.x == 0) *c.abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -238,21 +240,23 @@ __device__ __forceinline__ void init_barriers(const CtaSmem& c, const StreamPlan
 // the current weight tile, so their latency is covered by a whole segment of work.  (Keeping a
 // lane's activations of all its segments in registers for the whole CTA, possible for
 // K <= 4096, measured 1-2 us SLOWER: every CTA then asks for the same few lines at once.)
-template <typename OutT, int MT, bool RAW_I32>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename OutT, int MT, bool RAW_I32, int WPP>
+__global__ void __launch_bounds__(kPipes * WPP * 32 + 32, 1)
 w8a8_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const int8_t* __restrict__ xq,
                           const float* __restrict__ a_s, const float* __restrict__ w_s,
                           const OutT* __restrict__ bias, void* __restrict__ out, int M, int N, int K,
                           const StreamPlan p, int* status) {
+  constexpr int kCW = kPipes * WPP, kCT = kCW * 32;  // consumer warps / threads
+  constexpr int NTW = kNT / WPP;                     // 8-row MMA tiles per consumer warp
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const CtaSmem sm = carve(smem_raw, p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Share sh = share_of(N, blockIdx.x, gridDim.x);
-  if (threadIdx.x == kConsumerThreads) ptx::tma_prefetch_desc(&tm_w);
-  init_barriers(sm, p);
+  if (threadIdx.x == kCT) ptx::tma_prefetch_desc(&tm_w);
+  init_barriers(sm, p, WPP);
   ptx::grid_launch_dependents();
-  if (warp == kConsumerWarps) {
-    if (lane < kConsumerWarps)
+  if (warp == kCW) {
+    if (lane < kPipes)
       produce(&tm_w, p, sh, lane, ptx::smem_u32(sm.base) + lane * p.slots * p.slot_bytes,
               sm.full + lane * kMaxSlots, sm.empty + lane * kMaxSlots, sm.abort_flag);
     return;
@@ -260,18 +264,19 @@ w8a8_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const int8_t
   ptx::grid_dependency_wait();  // activations and their scales come from the previous kernel
 
   const int g = lane >> 2, t = lane & 3;
-  const uint8_t* ring = sm.base + warp * p.slots * p.slot_bytes;
-  uint64_t* full = sm.full + warp * kMaxSlots;
-  uint64_t* empty = sm.empty + warp * kMaxSlots;
+  const int pipe = warp % kPipes, part = warp / kPipes;  // part: which NTW tiles of the unit
+  const uint8_t* ring = sm.base + pipe * p.slots * p.slot_bytes;
+  uint64_t* full = sm.full + pipe * kMaxSlots;
+  uint64_t* empty = sm.empty + pipe * kMaxSlots;
   int* red = reinterpret_cast<int*>(sm.red);
   // swizzled positions of this lane's two 16-byte pieces in a 128-byte row whose index is g mod 8
   const int o0 = g * 128 + (((2 * t) ^ g) << 4), o1 = g * 128 + (((2 * t + 1) ^ g) << 4);
-  const int my_segs = (p.segs - warp + kConsumerWarps - 1) / kConsumerWarps;
+  const int my_segs = (p.segs - pipe + kPipes - 1) / kPipes;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
   // x[m][0..1] = pieces of token row m*16+g, x[m][2..3] = of token row m*16+g+8
   auto load_x = [&](int c, uint4 (&x)[MT][4]) {
-    const int k = (warp + kConsumerWarps * c) * kSeg + 32 * t;
+    const int k = (pipe + kPipes * c) * kSeg + 32 * t;
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
       const int r0 = m * 16 + g, r1 = r0 + 8;
@@ -291,11 +296,11 @@ w8a8_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const int8_t
   for (int u = 0; u < sh.units; ++u) {
     int ulo, rows;
     unit_range(sh, u, ulo, rows);
-    int acc[MT][kNT][4];
+    int acc[MT][NTW][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
-      for (int j = 0; j < kNT; ++j)
+      for (int j = 0; j < NTW; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[m][j][i] = 0;
 
@@ -307,10 +312,11 @@ w8a8_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const int8_t
       if (alive) {
         const uint8_t* ws = ring + slot * p.slot_bytes;
 #pragma unroll
-        for (int j = 0; j < kNT; ++j) {
-          if (j * 8 < rows) {
-            const uint4 w0 = *reinterpret_cast<const uint4*>(ws + j * 1024 + o0);
-            const uint4 w1 = *reinterpret_cast<const uint4*>(ws + j * 1024 + o1);
+        for (int j = 0; j < NTW; ++j) {
+          const int jj = part * NTW + j;  // tile of the unit
+          if (jj * 8 < rows) {
+            const uint4 w0 = *reinterpret_cast<const uint4*>(ws + jj * 1024 + o0);
+            const uint4 w1 = *reinterpret_cast<const uint4*>(ws + jj * 1024 + o1);
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
               // each pair of words is one k32 step: slots 4t..4t+3 and 16+4t..16+4t+3
@@ -338,21 +344,21 @@ w8a8_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const int8_t
     // C fragment: acc[m][j][0..1] = (token m*16+g, channels 8j+2t, +1), [2..3] = token + 8
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
-      int* r = red + warp * (16 * kUnitRows);
+      int* r = red + pipe * (16 * kUnitRows) + part * NTW * 8;
 #pragma unroll
-      for (int j = 0; j < kNT; ++j) {
+      for (int j = 0; j < NTW; ++j) {
         r[g * kUnitRows + j * 8 + 2 * t] = acc[m][j][0];
         r[g * kUnitRows + j * 8 + 2 * t + 1] = acc[m][j][1];
         r[(g + 8) * kUnitRows + j * 8 + 2 * t] = acc[m][j][2];
         r[(g + 8) * kUnitRows + j * 8 + 2 * t + 1] = acc[m][j][3];
       }
-      consumer_barrier();
-      for (int o = threadIdx.x; o < 16 * kUnitRows; o += kConsumerThreads) {
+      consumer_barrier<kCT>();
+      for (int o = threadIdx.x; o < 16 * kUnitRows; o += kCT) {
         const int tok = m * 16 + o / kUnitRows, ch = o % kUnitRows;
         if (tok >= M || ch >= rows) continue;
         int sum = 0;
 #pragma unroll
-        for (int wi = 0; wi < kConsumerWarps; ++wi) sum += red[wi * (16 * kUnitRows) + o];
+        for (int wi = 0; wi < kPipes; ++wi) sum += red[wi * (16 * kUnitRows) + o];
         const int n = ulo + ch;
         const size_t idx = static_cast<size_t>(tok) * N + n;
         if (RAW_I32) {
@@ -364,7 +370,7 @@ w8a8_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const int8_t
           reinterpret_cast<OutT*>(out)[idx] = from_float<OutT>(v);
         }
       }
-      consumer_barrier();
+      consumer_barrier<kCT>();
     }
   }
   if (threadIdx.x == 0 && *sm.abort_flag != 0)
@@ -374,20 +380,22 @@ w8a8_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const int8_t
 // ------------------------------------------------------------------------ W8A16
 // The lane's 32 activations of a segment are 64 contiguous bytes per token row.  Weight word i
 // of the lane (4 codes) meets activation words 2 i and 2 i + 1 (2 values each) in one k16 step.
-template <typename T, int MT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, int MT, int WPP>
+__global__ void __launch_bounds__(kPipes * WPP * 32 + 32, 1)
 w8a16_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const T* __restrict__ x,
                            const float* __restrict__ sc, const T* __restrict__ bias,
                            T* __restrict__ y, int M, int N, int K, const StreamPlan p, int* status) {
+  constexpr int kCW = kPipes * WPP, kCT = kCW * 32;  // consumer warps / threads
+  constexpr int NTW = kNT / WPP;                     // 8-row MMA tiles per consumer warp
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const CtaSmem sm = carve(smem_raw, p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Share sh = share_of(N, blockIdx.x, gridDim.x);
-  if (threadIdx.x == kConsumerThreads) ptx::tma_prefetch_desc(&tm_w);
-  init_barriers(sm, p);
+  if (threadIdx.x == kCT) ptx::tma_prefetch_desc(&tm_w);
+  init_barriers(sm, p, WPP);
   ptx::grid_launch_dependents();
-  if (warp == kConsumerWarps) {
-    if (lane < kConsumerWarps)
+  if (warp == kCW) {
+    if (lane < kPipes)
       produce(&tm_w, p, sh, lane, ptx::smem_u32(sm.base) + lane * p.slots * p.slot_bytes,
               sm.full + lane * kMaxSlots, sm.empty + lane * kMaxSlots, sm.abort_flag);
     return;
@@ -395,17 +403,18 @@ w8a16_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const T* __
   ptx::grid_dependency_wait();  // activations come from the previous kernel in the stream
 
   const int g = lane >> 2, t = lane & 3;
-  const uint8_t* ring = sm.base + warp * p.slots * p.slot_bytes;
-  uint64_t* full = sm.full + warp * kMaxSlots;
-  uint64_t* empty = sm.empty + warp * kMaxSlots;
+  const int pipe = warp % kPipes, part = warp / kPipes;  // part: which NTW tiles of the unit
+  const uint8_t* ring = sm.base + pipe * p.slots * p.slot_bytes;
+  uint64_t* full = sm.full + pipe * kMaxSlots;
+  uint64_t* empty = sm.empty + pipe * kMaxSlots;
   float* red = reinterpret_cast<float*>(sm.red);
   const int o0 = g * 128 + (((2 * t) ^ g) << 4), o1 = g * 128 + (((2 * t + 1) ^ g) << 4);
-  const int my_segs = (p.segs - warp + kConsumerWarps - 1) / kConsumerWarps;
+  const int my_segs = (p.segs - pipe + kPipes - 1) / kPipes;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
   // xa[m][0..3] = the 32 values of token row m*16+g, xb[m][0..3] = of token row m*16+g+8
   auto load_x = [&](int c, uint4 (&xa)[MT][4], uint4 (&xb)[MT][4]) {
-    const int k = (warp + kConsumerWarps * c) * kSeg + 32 * t;
+    const int k = (pipe + kPipes * c) * kSeg + 32 * t;
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
       const int r0 = m * 16 + g, r1 = r0 + 8;
@@ -427,11 +436,11 @@ w8a16_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const T* __
   for (int u = 0; u < sh.units; ++u) {
     int ulo, rows;
     unit_range(sh, u, ulo, rows);
-    float acc[MT][kNT][4];
+    float acc[MT][NTW][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
-      for (int j = 0; j < kNT; ++j)
+      for (int j = 0; j < NTW; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
 
@@ -444,10 +453,11 @@ w8a16_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const T* __
       if (alive) {
         const uint8_t* ws = ring + slot * p.slot_bytes;
 #pragma unroll
-        for (int j = 0; j < kNT; ++j) {
-          if (j * 8 < rows) {
-            const uint4 w0 = *reinterpret_cast<const uint4*>(ws + j * 1024 + o0);
-            const uint4 w1 = *reinterpret_cast<const uint4*>(ws + j * 1024 + o1);
+        for (int j = 0; j < NTW; ++j) {
+          const int jj = part * NTW + j;  // tile of the unit
+          if (jj * 8 < rows) {
+            const uint4 w0 = *reinterpret_cast<const uint4*>(ws + jj * 1024 + o0);
+            const uint4 w1 = *reinterpret_cast<const uint4*>(ws + jj * 1024 + o1);
             const uint2 e0 = expand4<T>(w0.x), e1 = expand4<T>(w0.y), e2 = expand4<T>(w0.z),
                         e3 = expand4<T>(w0.w), e4 = expand4<T>(w1.x), e5 = expand4<T>(w1.y),
                         e6 = expand4<T>(w1.z), e7 = expand4<T>(w1.w);
@@ -478,27 +488,27 @@ w8a16_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const T* __
 
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
-      float* r = red + warp * (16 * kUnitRows);
+      float* r = red + pipe * (16 * kUnitRows) + part * NTW * 8;
 #pragma unroll
-      for (int j = 0; j < kNT; ++j) {
+      for (int j = 0; j < NTW; ++j) {
         r[g * kUnitRows + j * 8 + 2 * t] = acc[m][j][0];
         r[g * kUnitRows + j * 8 + 2 * t + 1] = acc[m][j][1];
         r[(g + 8) * kUnitRows + j * 8 + 2 * t] = acc[m][j][2];
         r[(g + 8) * kUnitRows + j * 8 + 2 * t + 1] = acc[m][j][3];
       }
-      consumer_barrier();
-      for (int o = threadIdx.x; o < 16 * kUnitRows; o += kConsumerThreads) {
+      consumer_barrier<kCT>();
+      for (int o = threadIdx.x; o < 16 * kUnitRows; o += kCT) {
         const int tok = m * 16 + o / kUnitRows, ch = o % kUnitRows;
         if (tok >= M || ch >= rows) continue;
         float sum = 0.f;
 #pragma unroll
-        for (int wi = 0; wi < kConsumerWarps; ++wi)
+        for (int wi = 0; wi < kPipes; ++wi)
           sum = __fadd_rn(sum, red[wi * (16 * kUnitRows) + o]);  // fixed order
         const int n = ulo + ch;
         const float b = bias != nullptr ? to_float<T>(bias[n]) : 0.f;
         y[static_cast<size_t>(tok) * N + n] = from_float<T>(__fadd_rn(__fmul_rn(sum, sc[n]), b));
       }
-      consumer_barrier();
+      consumer_barrier<kCT>();
     }
   }
   if (threadIdx.x == 0 && *sm.abort_flag != 0)
@@ -518,7 +528,7 @@ bool make_plan(int M, int N, int K, bool a16, StreamPlan& p) {
   p.tx_bytes = p.unit_rows * 128;
   p.segs = (K + kSeg - 1) / kSeg;
   const int fixed = kRedBytes + kBarBytes + 16 + 1024;  // + slack for the 1 KB alignment
-  p.slots = (kSmemLimit - fixed) / (kConsumerWarps * p.slot_bytes);
+  p.slots = (kSmemLimit - fixed) / (kPipes * p.slot_bytes);
   if (p.slots > kMaxSlots) p.slots = kMaxSlots;
   const int want = debug_knob(B200Q_KNOB_BULK_SLOTS, 0);  // tuning: a shallower ring
   if (want >= 2 && want < p.slots) p.slots = want;
@@ -528,13 +538,13 @@ bool make_plan(int M, int N, int K, bool a16, StreamPlan& p) {
 }
 
 size_t plan_smem(const StreamPlan& p) {
-  return static_cast<size_t>(kConsumerWarps) * p.slots * p.slot_bytes + kRedBytes + kBarBytes + 16 + 1024;
+  return static_cast<size_t>(kPipes) * p.slots * p.slot_bytes + kRedBytes + kBarBytes + 16 + 1024;
 }
 
 // The kernel is a template ARGUMENT, so every kernel has a flag of its own (kernels of one
 // signature share a function-pointer type).
 template <auto kernel, typename... Args>
-cudaError_t launch_stream(int grid, size_t smem, cudaStream_t stream, Args... args) {
+cudaError_t launch_stream(int grid, int threads, size_t smem, cudaStream_t stream, Args... args) {
   static bool raised[64] = {false};  // per device
   int dev = 0;
   cudaGetDevice(&dev);
@@ -543,7 +553,7 @@ cudaError_t launch_stream(int grid, size_t smem, cudaStream_t stream, Args... ar
     if (e != cudaSuccess) return e;
     if (dev < 64) raised[dev] = true;
   }
-  return launch_overlapped(kernel, dim3(grid), dim3(kThreads), smem, stream, args...);
+  return launch_overlapped(kernel, dim3(grid), dim3(threads), smem, stream, args...);
 }
 
 }  // namespace
@@ -572,24 +582,29 @@ cudaError_t launch_w8a8_bulk_decode(const GemmArgs& a) {
   const int grid = grid_for(a.N);
   const size_t smem = plan_smem(p);
   cudaError_t e = cudaSuccess;
-#define B200Q_STREAM_A8(MT)                                                                        \
+#define B200Q_STREAM_A8(MT, WPP)                                                                   \
   if (a.acc_out != nullptr)                                                                        \
-    e = launch_stream<w8a8_stream_decode_kernel<__nv_bfloat16, MT, true>>(                        \
-        grid, smem, a.stream, tm_w, xq, a.a_scales, a.w_scales,                                   \
-        static_cast<const __nv_bfloat16*>(nullptr), static_cast<void*>(a.acc_out), a.M, a.N, a.K, p,     \
-        a.status);                                                                                  \
+    e = launch_stream<w8a8_stream_decode_kernel<__nv_bfloat16, MT, true, WPP>>(                     \
+        grid, kPipes * WPP * 32 + 32, smem, a.stream, tm_w, xq, a.a_scales, a.w_scales,             \
+        static_cast<const __nv_bfloat16*>(nullptr), static_cast<void*>(a.acc_out), a.M, a.N, a.K,   \
+        p, a.status);                                                                               \
   else if (a.dtype == B200Q_DTYPE_BF16)                                                            \
-    e = launch_stream<w8a8_stream_decode_kernel<__nv_bfloat16, MT, false>>(                        \
-        grid, smem, a.stream, tm_w, xq, a.a_scales, a.w_scales,                                   \
-        static_cast<const __nv_bfloat16*>(a.bias), a.y, a.M, a.N, a.K, p, a.status);                     \
+    e = launch_stream<w8a8_stream_decode_kernel<__nv_bfloat16, MT, false, WPP>>(                    \
+        grid, kPipes * WPP * 32 + 32, smem, a.stream, tm_w, xq, a.a_scales, a.w_scales,             \
+        static_cast<const __nv_bfloat16*>(a.bias), a.y, a.M, a.N, a.K, p, a.status);                \
   else                                                                                             \
-    e = launch_stream<w8a8_stream_decode_kernel<__half, MT, false>>(                            \
-        grid, smem, a.stream, tm_w, xq, a.a_scales, a.w_scales, static_cast<const __half*>(a.bias), \
-        a.y, a.M, a.N, a.K, p, a.status)
-  if (a.M <= 16) {
-    B200Q_STREAM_A8(1);
+    e = launch_stream<w8a8_stream_decode_kernel<__half, MT, false, WPP>>(                           \
+        grid, kPipes * WPP * 32 + 32, smem, a.stream, tm_w, xq, a.a_scales, a.w_scales,             \
+        static_cast<const __half*>(a.bias), a.y, a.M, a.N, a.K, p, a.status)
+  // One token tile: two consumer warps per ring (more warps to cover the latencies of the
+  // ring waits and the activation loads: 3-9 % on the 8B projections).  Two token tiles do not
+  // fit the register file of 17 warps without spilling (M = 32: 28 against 17.6 us).
+  if (a.M <= 16 && debug_knob(B200Q_KNOB_BULK_WPP, 2) == 2) {
+    B200Q_STREAM_A8(1, 2);
+  } else if (a.M <= 16) {
+    B200Q_STREAM_A8(1, 1);
   } else {
-    B200Q_STREAM_A8(2);
+    B200Q_STREAM_A8(2, 1);
   }
 #undef B200Q_STREAM_A8
   if (e == cudaSuccess) count_launch();
@@ -604,17 +619,20 @@ cudaError_t launch_w8a16_bulk_decode(const GemmArgs& a) {
   const int grid = grid_for(a.N);
   const size_t smem = plan_smem(p);
   cudaError_t e = cudaSuccess;
-#define B200Q_STREAM_A16(MT)                                                                       \
+#define B200Q_STREAM_A16(MT, WPP)                                                                  \
   if (a.dtype == B200Q_DTYPE_BF16)                                                                 \
-    e = launch_stream<w8a16_stream_decode_kernel<__nv_bfloat16, MT>>(                               \
-        grid, smem, a.stream, tm_w, static_cast<const __nv_bfloat16*>(a.x), a.w_scales,             \
-        static_cast<const __nv_bfloat16*>(a.bias), static_cast<__nv_bfloat16*>(a.y), a.M, a.N, a.K, \
-        p, a.status);                                   \
+    e = launch_stream<w8a16_stream_decode_kernel<__nv_bfloat16, MT, WPP>>(                          \
+        grid, kPipes * WPP * 32 + 32, smem, a.stream, tm_w, static_cast<const __nv_bfloat16*>(a.x), \
+        a.w_scales, static_cast<const __nv_bfloat16*>(a.bias), static_cast<__nv_bfloat16*>(a.y),    \
+        a.M, a.N, a.K, p, a.status);                                                                \
   else                                                                                             \
-    e = launch_stream<w8a16_stream_decode_kernel<__half, MT>>(                                      \
-        grid, smem, a.stream, tm_w, static_cast<const __half*>(a.x), a.w_scales,                    \
-        static_cast<const __half*>(a.bias), static_cast<__half*>(a.y), a.M, a.N, a.K, p, a.status)
-  B200Q_STREAM_A16(1);
+    e = launch_stream<w8a16_stream_decode_kernel<__half, MT, WPP>>(                                 \
+        grid, kPipes * WPP * 32 + 32, smem, a.stream, tm_w, static_cast<const __half*>(a.x),        \
+        a.w_scales, static_cast<const __half*>(a.bias), static_cast<__half*>(a.y), a.M, a.N, a.K,   \
+        p, a.status)
+  // one consumer warp per ring: with two, each pair loads the activations twice and the 16-bit
+  // fragments spill (gate_up at M = 1: 37.5 against 34.2 us)
+  B200Q_STREAM_A16(1, 1);
 #undef B200Q_STREAM_A16
   if (e == cudaSuccess) count_launch();
   return e;
