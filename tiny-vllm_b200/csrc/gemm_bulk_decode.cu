@@ -32,7 +32,8 @@
 //   W8A8  m16n8k32 s8, exact int32 sums, then (float(acc) * a_s[m]) * w_s[n] + bias[n]
 //         (nanovllm/quantization/csrc/w8a8_gemm.cu:165-183, 387-390)
 //   W8A16 m16n8k16 f16/bf16 after an exact in-register expansion of the codes, fp32 sums of
-//         x * float(q), then acc * s[n] + bias[n]
+//         x * float(q), then acc * s[n] + bias[n]; for at most 8 tokens the channels take the
+//         16-row side of the MMA and the tokens the 8-column side (half the MMAs)
 //         (nanovllm/quantization/csrc/int8_weight_only_gemm.cu:258-292)
 // Rows and columns outside the matrices are zero-filled by TMA, so ragged K needs no masks.
 // Every mbarrier wait is bounded; a wait that runs out stops the CTA's loops (the consumer
@@ -515,6 +516,136 @@ w8a16_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const T* __
     atomicCAS(status, 0, 0x900 | (static_cast<int>(blockIdx.x) << 12));
 }
 
+// ------------------------------------------------- W8A16, at most 8 tokens
+// With 8 tokens or fewer the CHANNELS go on the 16-row side of the MMA and the tokens on its
+// 8-column side: one m16n8k16 covers 16 channels (rows g and g + 8 of a pair of 8-row tiles),
+// so a segment costs 24 MMAs per warp instead of 48, and a lane loads one token row (g) instead
+// of two.  Everything else — rings, producer, expansion, fixed-order reduction — is as above.
+template <typename T>
+__global__ void __launch_bounds__(kPipes * 32 + 32, 1)
+w8a16_stream_decode_m8_kernel(const __grid_constant__ CUtensorMap tm_w, const T* __restrict__ x,
+                              const float* __restrict__ sc, const T* __restrict__ bias,
+                              T* __restrict__ y, int M, int N, int K, const StreamPlan p,
+                              int* status) {
+  constexpr int kCT = kPipes * 32;
+  constexpr int kMT16 = kNT / 2;  // 16-channel MMA tiles per unit
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const CtaSmem sm = carve(smem_raw, p);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const Share sh = share_of(N, blockIdx.x, gridDim.x);
+  if (threadIdx.x == kCT) ptx::tma_prefetch_desc(&tm_w);
+  init_barriers(sm, p, 1);
+  ptx::grid_launch_dependents();
+  if (warp == kPipes) {
+    if (lane < kPipes)
+      produce(&tm_w, p, sh, lane, ptx::smem_u32(sm.base) + lane * p.slots * p.slot_bytes,
+              sm.full + lane * kMaxSlots, sm.empty + lane * kMaxSlots, sm.abort_flag);
+    return;
+  }
+  ptx::grid_dependency_wait();  // activations come from the previous kernel in the stream
+
+  const int g = lane >> 2, t = lane & 3;
+  const int pipe = warp;
+  const uint8_t* ring = sm.base + pipe * p.slots * p.slot_bytes;
+  uint64_t* full = sm.full + pipe * kMaxSlots;
+  uint64_t* empty = sm.empty + pipe * kMaxSlots;
+  float* red = reinterpret_cast<float*>(sm.red);
+  const int o0 = g * 128 + (((2 * t) ^ g) << 4), o1 = g * 128 + (((2 * t + 1) ^ g) << 4);
+  const int my_segs = (p.segs - pipe + kPipes - 1) / kPipes;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+  // the 32 values of token row g of the lane's part of segment c
+  auto load_x = [&](int c, uint4 (&xv)[4]) {
+    const int k = (pipe + kPipes * c) * kSeg + 32 * t;
+    const T* p0 = x + static_cast<size_t>(g) * K + k;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      xv[j] = (g < M && k + 8 * j < K) ? __ldg(reinterpret_cast<const uint4*>(p0) + j) : zero;
+  };
+
+  uint4 xc[4], xn[4];
+  if (sh.units > 0 && my_segs > 0) load_x(0, xc);
+  bool alive = true;
+  int it = 0;
+  for (int u = 0; u < sh.units; ++u) {
+    int ulo, rows;
+    unit_range(sh, u, ulo, rows);
+    float acc[kMT16][4];
+#pragma unroll
+    for (int q = 0; q < kMT16; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[q][i] = 0.f;
+
+    for (int c = 0; c < my_segs; ++c, ++it) {
+      if (c + 1 < my_segs || u + 1 < sh.units) load_x(c + 1 < my_segs ? c + 1 : 0, xn);
+      const int slot = it % p.slots;
+      if (alive)
+        alive = ptx::mbar_wait(ptx::smem_u32(full + slot), static_cast<uint32_t>((it / p.slots) & 1),
+                               sm.abort_flag);
+      if (alive) {
+        const uint8_t* ws = ring + slot * p.slot_bytes;
+#pragma unroll
+        for (int q = 0; q < kMT16; ++q) {
+          if (q * 16 < rows) {
+            // channel 16 q + g (tile 2 q) and channel 16 q + 8 + g (tile 2 q + 1)
+            const uint4 a0 = *reinterpret_cast<const uint4*>(ws + (2 * q) * 1024 + o0);
+            const uint4 a1 = *reinterpret_cast<const uint4*>(ws + (2 * q) * 1024 + o1);
+            const uint4 b0 = *reinterpret_cast<const uint4*>(ws + (2 * q + 1) * 1024 + o0);
+            const uint4 b1 = *reinterpret_cast<const uint4*>(ws + (2 * q + 1) * 1024 + o1);
+            uint2 ea, eb;
+            // weight word i of the lane meets activation words 2 i and 2 i + 1
+            ea = expand4<T>(a0.x); eb = expand4<T>(b0.x);
+            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[0].x, xc[0].y);
+            ea = expand4<T>(a0.y); eb = expand4<T>(b0.y);
+            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[0].z, xc[0].w);
+            ea = expand4<T>(a0.z); eb = expand4<T>(b0.z);
+            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[1].x, xc[1].y);
+            ea = expand4<T>(a0.w); eb = expand4<T>(b0.w);
+            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[1].z, xc[1].w);
+            ea = expand4<T>(a1.x); eb = expand4<T>(b1.x);
+            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[2].x, xc[2].y);
+            ea = expand4<T>(a1.y); eb = expand4<T>(b1.y);
+            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[2].z, xc[2].w);
+            ea = expand4<T>(a1.z); eb = expand4<T>(b1.z);
+            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[3].x, xc[3].y);
+            ea = expand4<T>(a1.w); eb = expand4<T>(b1.w);
+            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[3].z, xc[3].w);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(empty + slot));
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) xc[i] = xn[i];
+    }
+
+    // C fragment: acc[q][0..1] = (channel 16q+g, tokens 2t, 2t+1), [2..3] = channel 16q+8+g
+    float* r = red + pipe * (16 * kUnitRows);  // used as [8 tokens][48 channels]
+#pragma unroll
+    for (int q = 0; q < kMT16; ++q) {
+      r[(2 * t) * kUnitRows + 16 * q + g] = acc[q][0];
+      r[(2 * t + 1) * kUnitRows + 16 * q + g] = acc[q][1];
+      r[(2 * t) * kUnitRows + 16 * q + 8 + g] = acc[q][2];
+      r[(2 * t + 1) * kUnitRows + 16 * q + 8 + g] = acc[q][3];
+    }
+    consumer_barrier<kCT>();
+    for (int o = threadIdx.x; o < 8 * kUnitRows; o += kCT) {
+      const int tok = o / kUnitRows, ch = o % kUnitRows;
+      if (tok >= M || ch >= rows) continue;
+      float sum = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < kPipes; ++wi)
+        sum = __fadd_rn(sum, red[wi * (16 * kUnitRows) + o]);  // fixed order
+      const int n = ulo + ch;
+      const float b = bias != nullptr ? to_float<T>(bias[n]) : 0.f;
+      y[static_cast<size_t>(tok) * N + n] = from_float<T>(__fadd_rn(__fmul_rn(sum, sc[n]), b));
+    }
+    consumer_barrier<kCT>();
+  }
+  if (threadIdx.x == 0 && *sm.abort_flag != 0)
+    atomicCAS(status, 0, 0x900 | (static_cast<int>(blockIdx.x) << 12));
+}
+
 // ------------------------------------------------------------------------ host
 int grid_for(int N) { return N < sm_count() ? N : sm_count(); }
 
@@ -632,7 +763,19 @@ cudaError_t launch_w8a16_bulk_decode(const GemmArgs& a) {
         p, a.status)
   // one consumer warp per ring: with two, each pair loads the activations twice and the 16-bit
   // fragments spill (gate_up at M = 1: 37.5 against 34.2 us)
-  B200Q_STREAM_A16(1, 1);
+  if (a.M <= 8 && debug_knob(B200Q_KNOB_BULK_WPP, 0) != 1) {  // knob 1: the 16-token kernel, for tests
+    if (a.dtype == B200Q_DTYPE_BF16)
+      e = launch_stream<w8a16_stream_decode_m8_kernel<__nv_bfloat16>>(
+          grid, kPipes * 32 + 32, smem, a.stream, tm_w, static_cast<const __nv_bfloat16*>(a.x), a.w_scales,
+          static_cast<const __nv_bfloat16*>(a.bias), static_cast<__nv_bfloat16*>(a.y), a.M, a.N, a.K, p,
+          a.status);
+    else
+      e = launch_stream<w8a16_stream_decode_m8_kernel<__half>>(
+          grid, kPipes * 32 + 32, smem, a.stream, tm_w, static_cast<const __half*>(a.x), a.w_scales,
+          static_cast<const __half*>(a.bias), static_cast<__half*>(a.y), a.M, a.N, a.K, p, a.status);
+  } else {
+    B200Q_STREAM_A16(1, 1);
+  }
 #undef B200Q_STREAM_A16
   if (e == cudaSuccess) count_launch();
   return e;
