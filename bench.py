@@ -360,6 +360,12 @@ def extras(detail, work, ws, dev, batch_us, peaks):
         t_16 = eager_us(lambda: ref.cuda.native_int8_weight_only_linear(w["x"], q, s, None))
         rg[w["name"]] = {"quantize_us": t_q, "w8a8_gemm_us": t_g, "w8a16_gemm_us": t_16,
                          "w8a8_gemm_tops": w["ops"] / t_g / 1e6}
+        # the same kernels on a decode batch of 16 tokens (this library: detail.<shape>.decode)
+        x16 = w["x"][:16].contiguous()
+        xq16, as16 = ref.utils.quantize_int8_per_row_dynamic(x16)
+        rg[w["name"]]["decode_m16"] = {
+            "w8a8_gemm_us": eager_us(lambda: ref.cuda.native_w8a8_linear(xq16, as16, q, s, None, torch.bfloat16), 20),
+            "w8a16_gemm_us": eager_us(lambda: ref.cuda.native_int8_weight_only_linear(x16, q, s, None), 20)}
         step_us += t_q + t_g
     rg["step_us"] = step_us
     rg["step_tops"] = sum(w["ops"] for w in work) / step_us / 1e6
