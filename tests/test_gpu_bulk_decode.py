@@ -84,6 +84,13 @@ def test_w8a16_within_the_gates(M, N, K, dtype):
     # the two kernels cut K differently, so they differ in the last bits only
     m = O.tensor_metrics(y_regs, y)
     assert m["relative_l2"] <= 2e-3, m
+    if M <= 8:
+        # up to 8 tokens run the form with the channels on the 16-row side of the MMA; knob
+        # BULK_WPP = 1 runs the 16-token form on the same problem
+        with forced_path("mma"), knobs(BULK_DECODE=2, BULK_WPP=1):
+            y_16 = apply_int8_weight_only_linear(*dev)
+        m = O.tensor_metrics(y_16, y)
+        assert m["relative_l2"] <= 2e-3, m
     assert device_status_ok()
 
 

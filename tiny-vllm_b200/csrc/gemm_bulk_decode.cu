@@ -137,8 +137,10 @@ __device__ __forceinline__ uint2 expand4<__nv_bfloat16>(uint32_t w) {
                                             __uint_as_float(__byte_perm(t, 0x4B000000u, 0x7541))), m);
   const float2 f23 = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7542)),
                                             __uint_as_float(__byte_perm(t, 0x4B000000u, 0x7543))), m);
-  const __nv_bfloat162 a = __floats2bfloat162_rn(f01.x, f01.y), b = __floats2bfloat162_rn(f23.x, f23.y);
-  return make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+  // the sums are integers of at most 8 significant bits: their bf16 form is the upper half of
+  // the fp32 word, taken with a byte permute (the packing conversion runs on a slower pipe)
+  return make_uint2(__byte_perm(__float_as_uint(f01.x), __float_as_uint(f01.y), 0x7632),
+                    __byte_perm(__float_as_uint(f23.x), __float_as_uint(f23.y), 0x7632));
 }
 
 
@@ -519,24 +521,28 @@ w8a16_stream_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const T* __
 // ------------------------------------------------- W8A16, at most 8 tokens
 // With 8 tokens or fewer the CHANNELS go on the 16-row side of the MMA and the tokens on its
 // 8-column side: one m16n8k16 covers 16 channels (rows g and g + 8 of a pair of 8-row tiles),
-// so a segment costs 24 MMAs per warp instead of 48, and a lane loads one token row (g) instead
-// of two.  Everything else — rings, producer, expansion, fixed-order reduction — is as above.
-template <typename T>
-__global__ void __launch_bounds__(kPipes * 32 + 32, 1)
+// so a segment costs 24 MMAs instead of 48, and a lane loads one token row (g) instead of two.
+// WPP = 2 (not instantiated: measured no faster) would let two consumer warps per ring split the
+// lane's eight weight words of a segment, the first and the second 16-byte piece with the
+// matching halves of the activations.  Everything else — rings, producer, expansion,
+// fixed-order reduction — is as above.
+template <typename T, int WPP>
+__global__ void __launch_bounds__(kPipes * WPP * 32 + 32, 1)
 w8a16_stream_decode_m8_kernel(const __grid_constant__ CUtensorMap tm_w, const T* __restrict__ x,
                               const float* __restrict__ sc, const T* __restrict__ bias,
                               T* __restrict__ y, int M, int N, int K, const StreamPlan p,
                               int* status) {
-  constexpr int kCT = kPipes * 32;
-  constexpr int kMT16 = kNT / 2;  // 16-channel MMA tiles per unit
+  constexpr int kCW = kPipes * WPP, kCT = kCW * 32;
+  constexpr int kMT16 = kNT / 2;   // 16-channel MMA tiles per unit
+  constexpr int kHalves = 2 / WPP; // 16-byte weight pieces per lane and warp
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const CtaSmem sm = carve(smem_raw, p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Share sh = share_of(N, blockIdx.x, gridDim.x);
   if (threadIdx.x == kCT) ptx::tma_prefetch_desc(&tm_w);
-  init_barriers(sm, p, 1);
+  init_barriers(sm, p, WPP);
   ptx::grid_launch_dependents();
-  if (warp == kPipes) {
+  if (warp == kCW) {
     if (lane < kPipes)
       produce(&tm_w, p, sh, lane, ptx::smem_u32(sm.base) + lane * p.slots * p.slot_bytes,
               sm.full + lane * kMaxSlots, sm.empty + lane * kMaxSlots, sm.abort_flag);
@@ -545,25 +551,29 @@ w8a16_stream_decode_m8_kernel(const __grid_constant__ CUtensorMap tm_w, const T*
   ptx::grid_dependency_wait();  // activations come from the previous kernel in the stream
 
   const int g = lane >> 2, t = lane & 3;
-  const int pipe = warp;
+  const int pipe = warp % kPipes, part = warp / kPipes;  // part: which piece (WPP = 2)
   const uint8_t* ring = sm.base + pipe * p.slots * p.slot_bytes;
   uint64_t* full = sm.full + pipe * kMaxSlots;
   uint64_t* empty = sm.empty + pipe * kMaxSlots;
   float* red = reinterpret_cast<float*>(sm.red);
-  const int o0 = g * 128 + (((2 * t) ^ g) << 4), o1 = g * 128 + (((2 * t + 1) ^ g) << 4);
+  // swizzled position of the lane's piece(s): piece 2 t + h of a row whose index is g mod 8
+  int off[kHalves];
+#pragma unroll
+  for (int h = 0; h < kHalves; ++h)
+    off[h] = g * 128 + (((2 * t + (WPP == 2 ? part : h)) ^ g) << 4);
   const int my_segs = (p.segs - pipe + kPipes - 1) / kPipes;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-  // the 32 values of token row g of the lane's part of segment c
-  auto load_x = [&](int c, uint4 (&xv)[4]) {
-    const int k = (pipe + kPipes * c) * kSeg + 32 * t;
+  // token row g: the 16 values that meet piece h are activation pieces 2 h and 2 h + 1
+  auto load_x = [&](int c, uint4 (&xv)[2 * kHalves]) {
+    const int k = (pipe + kPipes * c) * kSeg + 32 * t + (WPP == 2 ? 16 * part : 0);
     const T* p0 = x + static_cast<size_t>(g) * K + k;
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < 2 * kHalves; ++j)
       xv[j] = (g < M && k + 8 * j < K) ? __ldg(reinterpret_cast<const uint4*>(p0) + j) : zero;
   };
 
-  uint4 xc[4], xn[4];
+  uint4 xc[2 * kHalves], xn[2 * kHalves];
   if (sh.units > 0 && my_segs > 0) load_x(0, xc);
   bool alive = true;
   int it = 0;
@@ -587,40 +597,35 @@ w8a16_stream_decode_m8_kernel(const __grid_constant__ CUtensorMap tm_w, const T*
 #pragma unroll
         for (int q = 0; q < kMT16; ++q) {
           if (q * 16 < rows) {
-            // channel 16 q + g (tile 2 q) and channel 16 q + 8 + g (tile 2 q + 1)
-            const uint4 a0 = *reinterpret_cast<const uint4*>(ws + (2 * q) * 1024 + o0);
-            const uint4 a1 = *reinterpret_cast<const uint4*>(ws + (2 * q) * 1024 + o1);
-            const uint4 b0 = *reinterpret_cast<const uint4*>(ws + (2 * q + 1) * 1024 + o0);
-            const uint4 b1 = *reinterpret_cast<const uint4*>(ws + (2 * q + 1) * 1024 + o1);
-            uint2 ea, eb;
-            // weight word i of the lane meets activation words 2 i and 2 i + 1
-            ea = expand4<T>(a0.x); eb = expand4<T>(b0.x);
-            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[0].x, xc[0].y);
-            ea = expand4<T>(a0.y); eb = expand4<T>(b0.y);
-            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[0].z, xc[0].w);
-            ea = expand4<T>(a0.z); eb = expand4<T>(b0.z);
-            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[1].x, xc[1].y);
-            ea = expand4<T>(a0.w); eb = expand4<T>(b0.w);
-            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[1].z, xc[1].w);
-            ea = expand4<T>(a1.x); eb = expand4<T>(b1.x);
-            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[2].x, xc[2].y);
-            ea = expand4<T>(a1.y); eb = expand4<T>(b1.y);
-            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[2].z, xc[2].w);
-            ea = expand4<T>(a1.z); eb = expand4<T>(b1.z);
-            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[3].x, xc[3].y);
-            ea = expand4<T>(a1.w); eb = expand4<T>(b1.w);
-            mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, xc[3].z, xc[3].w);
+#pragma unroll
+            for (int h = 0; h < kHalves; ++h) {
+              // channel 16 q + g (tile 2 q) and channel 16 q + 8 + g (tile 2 q + 1)
+              const uint4 a = *reinterpret_cast<const uint4*>(ws + (2 * q) * 1024 + off[h]);
+              const uint4 b = *reinterpret_cast<const uint4*>(ws + (2 * q + 1) * 1024 + off[h]);
+              const uint4 x0 = xc[2 * h], x1 = xc[2 * h + 1];
+              uint2 ea, eb;
+              // weight word i of the piece meets activation words 2 i and 2 i + 1
+              ea = expand4<T>(a.x); eb = expand4<T>(b.x);
+              mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, x0.x, x0.y);
+              ea = expand4<T>(a.y); eb = expand4<T>(b.y);
+              mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, x0.z, x0.w);
+              ea = expand4<T>(a.z); eb = expand4<T>(b.z);
+              mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, x1.x, x1.y);
+              ea = expand4<T>(a.w); eb = expand4<T>(b.w);
+              mma_16<T>(acc[q], ea.x, eb.x, ea.y, eb.y, x1.z, x1.w);
+            }
           }
         }
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(empty + slot));
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) xc[i] = xn[i];
+      for (int i = 0; i < 2 * kHalves; ++i) xc[i] = xn[i];
     }
 
-    // C fragment: acc[q][0..1] = (channel 16q+g, tokens 2t, 2t+1), [2..3] = channel 16q+8+g
-    float* r = red + pipe * (16 * kUnitRows);  // used as [8 tokens][48 channels]
+    // C fragment: acc[q][0..1] = (channel 16q+g, tokens 2t, 2t+1), [2..3] = channel 16q+8+g.
+    // One partial tile [8 tokens][48 channels] per consumer warp.
+    float* r = red + warp * (8 * kUnitRows);
 #pragma unroll
     for (int q = 0; q < kMT16; ++q) {
       r[(2 * t) * kUnitRows + 16 * q + g] = acc[q][0];
@@ -634,8 +639,8 @@ w8a16_stream_decode_m8_kernel(const __grid_constant__ CUtensorMap tm_w, const T*
       if (tok >= M || ch >= rows) continue;
       float sum = 0.f;
 #pragma unroll
-      for (int wi = 0; wi < kPipes; ++wi)
-        sum = __fadd_rn(sum, red[wi * (16 * kUnitRows) + o]);  // fixed order
+      for (int wi = 0; wi < kCW; ++wi)
+        sum = __fadd_rn(sum, red[wi * (8 * kUnitRows) + o]);  // fixed order
       const int n = ulo + ch;
       const float b = bias != nullptr ? to_float<T>(bias[n]) : 0.f;
       y[static_cast<size_t>(tok) * N + n] = from_float<T>(__fadd_rn(__fmul_rn(sum, sc[n]), b));
@@ -763,14 +768,17 @@ cudaError_t launch_w8a16_bulk_decode(const GemmArgs& a) {
         p, a.status)
   // one consumer warp per ring: with two, each pair loads the activations twice and the 16-bit
   // fragments spill (gate_up at M = 1: 37.5 against 34.2 us)
-  if (a.M <= 8 && debug_knob(B200Q_KNOB_BULK_WPP, 0) != 1) {  // knob 1: the 16-token kernel, for tests
+  // knob BULK_WPP = 1: the 16-token kernel also for M <= 8 (tests compare the two forms)
+  if (a.M <= 8 && debug_knob(B200Q_KNOB_BULK_WPP, 0) != 1) {
+    // one warp per ring: splitting the lane's eight words between two warps (the template's
+    // WPP = 2) measured the same (26.95 against 27.11 us on gate_up)
     if (a.dtype == B200Q_DTYPE_BF16)
-      e = launch_stream<w8a16_stream_decode_m8_kernel<__nv_bfloat16>>(
+      e = launch_stream<w8a16_stream_decode_m8_kernel<__nv_bfloat16, 1>>(
           grid, kPipes * 32 + 32, smem, a.stream, tm_w, static_cast<const __nv_bfloat16*>(a.x), a.w_scales,
           static_cast<const __nv_bfloat16*>(a.bias), static_cast<__nv_bfloat16*>(a.y), a.M, a.N, a.K, p,
           a.status);
     else
-      e = launch_stream<w8a16_stream_decode_m8_kernel<__half>>(
+      e = launch_stream<w8a16_stream_decode_m8_kernel<__half, 1>>(
           grid, kPipes * 32 + 32, smem, a.stream, tm_w, static_cast<const __half*>(a.x), a.w_scales,
           static_cast<const __half*>(a.bias), static_cast<__half*>(a.y), a.M, a.N, a.K, p, a.status);
   } else {

@@ -215,8 +215,10 @@ __device__ __forceinline__ uint2 expand4<__nv_bfloat16>(uint32_t w) {
                                             __uint_as_float(__byte_perm(t, 0x4B000000u, 0x7541))), m);
   const float2 f23 = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7542)),
                                             __uint_as_float(__byte_perm(t, 0x4B000000u, 0x7543))), m);
-  const __nv_bfloat162 a = __floats2bfloat162_rn(f01.x, f01.y), b = __floats2bfloat162_rn(f23.x, f23.y);
-  return make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+  // the sums are integers of at most 8 significant bits: their bf16 form is the upper half of
+  // the fp32 word, taken with a byte permute (the packing conversion runs on a slower pipe)
+  return make_uint2(__byte_perm(__float_as_uint(f01.x), __float_as_uint(f01.y), 0x7632),
+                    __byte_perm(__float_as_uint(f23.x), __float_as_uint(f23.y), 0x7632));
 }
 
 // ------------------------------------------------------------------------- W8A8

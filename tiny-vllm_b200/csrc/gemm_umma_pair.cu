@@ -508,6 +508,34 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
+// Four int8 (one word) -> four values of type T (two words), exact, without integer-to-float
+// conversions: fp16: 0x6400 | u is the half 1024 + u (u = q + 128), minus 1152; bf16:
+// 0x4B000000 | u is the float 2^23 + u, minus 2^23 + 128, and the upper half of that fp32
+// word (an integer of at most 8 significant bits) is its bf16 form.
+template <typename T>
+__device__ __forceinline__ uint2 expand_word(uint32_t w);
+template <>
+__device__ __forceinline__ uint2 expand_word<__half>(uint32_t w) {
+  const uint32_t t = w ^ 0x80808080u;
+  uint32_t lo = __byte_perm(t, 0x64646464u, 0x4140);
+  uint32_t hi = __byte_perm(t, 0x64646464u, 0x4342);
+  const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+  const __half2 l = __hsub2(*reinterpret_cast<__half2*>(&lo), bias);
+  const __half2 h = __hsub2(*reinterpret_cast<__half2*>(&hi), bias);
+  return make_uint2(*reinterpret_cast<const uint32_t*>(&l), *reinterpret_cast<const uint32_t*>(&h));
+}
+template <>
+__device__ __forceinline__ uint2 expand_word<__nv_bfloat16>(uint32_t w) {
+  const uint32_t t = w ^ 0x80808080u;
+  const float2 m = make_float2(-8388736.f, -8388736.f);
+  const float2 f01 = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7540)),
+                                            __uint_as_float(__byte_perm(t, 0x4B000000u, 0x7541))), m);
+  const float2 f23 = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7542)),
+                                            __uint_as_float(__byte_perm(t, 0x4B000000u, 0x7543))), m);
+  return make_uint2(__byte_perm(__float_as_uint(f01.x), __float_as_uint(f01.y), 0x7632),
+                    __byte_perm(__float_as_uint(f23.x), __float_as_uint(f23.y), 0x7632));
+}
+
 // int8 [n] -> T [n], exact (|q| <= 128 has at most 8 significant bits).  16 codes per thread.
 template <typename T>
 __global__ void __launch_bounds__(256) w8a16_expand_kernel(const int8_t* __restrict__ q,
@@ -515,20 +543,11 @@ __global__ void __launch_bounds__(256) w8a16_expand_kernel(const int8_t* __restr
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) {
     const uint4 w = __ldg(reinterpret_cast<const uint4*>(q) + i);
-    const uint32_t in[4] = {w.x, w.y, w.z, w.w};
-    uint32_t o[8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float f[4];
-#pragma unroll
-      for (int b = 0; b < 4; ++b)
-        f[b] = static_cast<float>(static_cast<int>(static_cast<int8_t>((in[j] >> (8 * b)) & 0xFFu)));
-      o[2 * j] = pack2_rn<T>(make_float2(f[0], f[1]));
-      o[2 * j + 1] = pack2_rn<T>(make_float2(f[2], f[3]));
-    }
+    const uint2 e0 = expand_word<T>(w.x), e1 = expand_word<T>(w.y), e2 = expand_word<T>(w.z),
+                e3 = expand_word<T>(w.w);
     uint4* dst = reinterpret_cast<uint4*>(out) + 2 * i;
-    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    dst[0] = make_uint4(e0.x, e0.y, e1.x, e1.y);
+    dst[1] = make_uint4(e2.x, e2.y, e3.x, e3.y);
   }
 }
 
