@@ -23,7 +23,6 @@ and the caller then uses the two-kernel route.
 from __future__ import annotations
 
 import ctypes
-import os
 
 import torch
 import torch.distributed as dist
@@ -40,13 +39,18 @@ class PeerAllReduce:
     """Owns one symmetric data buffer and one symmetric flag pad for a process group."""
 
     def __init__(self, max_bytes: int, group=None, slots: int = 2, fused_bytes: int = 16 << 20,
-                 tiled_prefill: bool = False, code_bytes: int | None = None):
+                 tiled_prefill: bool = False, code_bytes: int | None = None,
+                 small_max_bytes: int | None = None, multimem: bool = False):
         """``max_bytes``: largest tensor a data slot holds.  ``slots``: number of rotating data
         slots, AT LEAST 2: the pull all-reduce (two ranks) leaves its input slot readable by
         the peer until the next collective, so the next partial result must go to another
         slot.  ``code_bytes``: size of each of the two int8 code buffers that
         :meth:`reduce_rmsnorm_quant` gathers into (default: ``max_bytes // 2``, i.e. the same
-        number of elements as a 16-bit data slot)."""
+        number of elements as a 16-bit data slot).  ``small_max_bytes``: largest tensor the
+        one-trip all-reduce takes (default by group size, see below).  ``multimem``: use the
+        in-switch reduction for large tensors where the fabric offers a multicast mapping and
+        the group has at least 4 ranks (off by default: it measured slower).  Nothing is read
+        from the environment."""
         import torch.distributed._symmetric_memory as symm_mem
 
         if not dist.is_initialized():
@@ -75,7 +79,7 @@ class PeerAllReduce:
         # twice the size, so the cross-over with the two-shot kernel falls as the group grows
         # (measured: 2 ranks about 2 MiB, 4 ranks about 400 KiB)
         default_small = (1 << 20) if self.world <= 2 else (256 << 10) if self.world <= 4 else (128 << 10)
-        self.small_max_bytes = int(os.environ.get("B200Q_SMALL_ALLREDUCE_BYTES", default_small))
+        self.small_max_bytes = int(small_max_bytes) if small_max_bytes is not None else default_small
         self._recv = symm_mem.empty(self.fused_bytes, dtype=torch.uint8, device=dev)
         self._recv.zero_()
         self._recv_hdl = symm_mem.rendezvous(self._recv, name)
@@ -85,7 +89,7 @@ class PeerAllReduce:
         # staging area of the fused prefill route (GEMM + reduce-scatter); the route is opt-in:
         # at TP=2 it measured 54 us against 56 us for GEMM + two-shot all-reduce (o_proj of
         # Qwen3-0.6B, 8192 tokens) — SM-issued stores over NVLink, not the GEMM, set its pace
-        self.tiled_prefill = tiled_prefill or os.environ.get("B200Q_TILED_ALLREDUCE", "0") == "1"
+        self.tiled_prefill = bool(tiled_prefill)
         self._stage = self._stage_hdl = None
         if self.tiled_prefill:
             self._stage = symm_mem.empty(self.slot_bytes, dtype=torch.uint8, device=dev)
@@ -103,8 +107,7 @@ class PeerAllReduce:
         self._data_ptrs = [int(p) for p in self._data_hdl.buffer_ptrs]
         # multicast mapping of the data buffer (0 when the fabric offers none): in-switch sums
         self._mc_ptr = int(getattr(self._data_hdl, "multicast_ptr", 0) or 0)
-        self.use_multimem = (self._mc_ptr != 0 and self.world >= 4
-                             and os.environ.get("B200Q_MULTIMEM_ALLREDUCE", "0") == "1")
+        self.use_multimem = bool(multimem) and self._mc_ptr != 0 and self.world >= 4
         pads = [int(p) for p in self._pad_hdl.buffer_ptrs]
         self._pad_arr = (ctypes.c_void_p * self.world)(*pads)
         self._recv_arr = (ctypes.c_void_p * self.world)(*[int(p) for p in self._recv_hdl.buffer_ptrs])

@@ -15,7 +15,6 @@ deliberate:
 """
 from __future__ import annotations
 
-import os
 import threading
 
 import torch
@@ -27,6 +26,16 @@ _DEFAULT_WORKSPACE_BYTES = 64 << 20
 
 _ws_lock = threading.Lock()
 _workspaces: dict[int, torch.Tensor] = {}
+_workspace_floor = [_DEFAULT_WORKSPACE_BYTES]
+
+
+def reserve_workspace(nbytes: int, device: torch.device | None = None) -> None:
+    """Makes the per-device scratch buffer at least ``nbytes`` large (call before CUDA-graph
+    capture when a model's shapes need more than the default 64 MiB; ``b200q_workspace_bytes``
+    of the C ABI gives the need of a shape).  With a ``device`` the buffer is allocated now."""
+    _workspace_floor[0] = max(_workspace_floor[0], int(nbytes))
+    if device is not None:
+        _workspace(torch.device(device), int(nbytes))
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -54,8 +63,8 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError(
                     f"b200q workspace of {nbytes} bytes requested during CUDA graph capture; "
-                    "run the shape once eagerly first or raise B200Q_WORKSPACE_BYTES")
-            want = max(nbytes, int(os.environ.get("B200Q_WORKSPACE_BYTES", _DEFAULT_WORKSPACE_BYTES)))
+                    "run the shape once eagerly first or call reserve_workspace() before capture")
+            want = max(nbytes, _workspace_floor[0])
             ws = torch.zeros(want, dtype=torch.uint8, device=torch.device("cuda", idx))
             _workspaces[idx] = ws
     return ws
