@@ -80,14 +80,14 @@ __device__ __noinline__ uint2 quant8_exact(const uint4 raw, float scale) {
 // 600 for random data) is redone with exact divisions.  Rounding uses the 1.5 * 2^23
 // trick: u = fma(v, 1/scale, 1.5 * 2^23) rounds p half-to-even to an integer and leaves
 // that integer in the low mantissa bits (two's complement), i.e. the low byte of u is the
-// int8 code; r = u - 1.5 * 2^23 is that integer exactly and fma(v, 1/scale, -r) the distance
-// to it.  |p| cannot exceed 127 (1 + 2^-22) because scale >= absmax / 127, so no clamp is
+// int8 code; r = u - 1.5 * 2^23 is that integer exactly (its negative is formed by one fused
+// multiply-add, -1 * u + 1.5 * 2^23, exact too) and fma(v, 1/scale, -r) the distance to it.  |p| cannot exceed 127 (1 + 2^-22) because scale >= absmax / 127, so no clamp is
 // needed.  Packed fp32x2 instructions round each half like the scalar ones.
 template <typename T>
 __device__ __forceinline__ uint2 quant8(const uint4 raw, float scale, float inv_scale) {
   const float2 inv2 = make_float2(inv_scale, inv_scale);
   const float2 magic = make_float2(12582912.0f, 12582912.0f);      // 1.5 * 2^23
-  const float2 neg_magic = make_float2(-12582912.0f, -12582912.0f);
+  const float2 minus_one = make_float2(-1.0f, -1.0f);
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   uint32_t ub[8];
   float worst = 0.f;
@@ -95,8 +95,8 @@ __device__ __forceinline__ uint2 quant8(const uint4 raw, float scale, float inv_
   for (int i = 0; i < 4; ++i) {
     const float2 v = unpack2<T>(w[i]);
     const float2 u = __ffma2_rn(v, inv2, magic);
-    const float2 r = __fadd2_rn(u, neg_magic);
-    const float2 d = __ffma2_rn(v, inv2, make_float2(-r.x, -r.y));
+    const float2 nr = __ffma2_rn(u, minus_one, magic);  // -(u - magic), exact: minus the rounded integer
+    const float2 d = __ffma2_rn(v, inv2, nr);
     worst = fmaxf(worst, fmaxf(fabsf(d.x), fabsf(d.y)));
     ub[2 * i] = __float_as_uint(u.x);
     ub[2 * i + 1] = __float_as_uint(u.y);
