@@ -38,8 +38,37 @@ def reserve_workspace(nbytes: int, device: torch.device | None = None) -> None:
         _workspace(torch.device(device), int(nbytes))
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_ptr(device: torch.device) -> int:
+    """Handle of the current stream of ``device`` (what ``torch.cuda.current_stream(device)
+    .cuda_stream`` returns, without building the stream object: this is on the path of every
+    linear of an eagerly executed step)."""
+    if _raw_stream is not None:
+        idx = device.index
+        return _raw_stream(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _on_device(device: torch.device):
+    """Device guard for a launch: nothing when ``device`` is the current device already (the
+    usual case; entering ``torch.cuda.device`` costs several microseconds per call)."""
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
@@ -71,7 +100,7 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
 
 
 def _require_cuda(*tensors: torch.Tensor) -> None:
-    if not torch.cuda.is_available() or not all(t.is_cuda for t in tensors):
+    if not all(t.is_cuda for t in tensors):
         raise RuntimeError(
             "b200q kernels need CUDA tensors on a B200; there is no CPU implementation of this path")
 
@@ -101,11 +130,12 @@ def quantize_activation_int8(x_2d: torch.Tensor) -> tuple[torch.Tensor, torch.Te
                 torch.empty((0,), dtype=torch.float32, device=x_2d.device))
     x_q = torch.empty((M, K), dtype=torch.int8, device=x_2d.device)
     a_scales = torch.empty((M,), dtype=torch.float32, device=x_2d.device)
-    with torch.cuda.device(x_2d.device):
+    with _on_device(x_2d.device):
         rc = _lib.lib().b200q_act_quant_i8(x_2d.data_ptr(), x_2d.stride(0), _DTYPE_IDS[x_2d.dtype],
                                            x_q.data_ptr(), a_scales.data_ptr(), M, K,
                                            _stream_ptr(x_2d.device))
-    _lib.check(rc, "b200q_act_quant_i8", f"M={M} K={K}")
+    if rc:
+        _lib.check(rc, "b200q_act_quant_i8", f"M={M} K={K}")
     return x_q, a_scales
 
 
@@ -135,13 +165,14 @@ def add_rmsnorm_quantize_int8(x: torch.Tensor, weight: torch.Tensor, eps: float,
     a_s = torch.empty((M,), dtype=torch.float32, device=x.device)
     new_res = torch.empty_like(x2) if residual is not None else None
     normed = torch.empty_like(x2) if return_normed else None
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         rc = _lib.lib().b200q_add_rmsnorm_quant_i8(
             x2.data_ptr(), None if r2 is None else r2.data_ptr(), weight.contiguous().data_ptr(),
             float(eps), None if new_res is None else new_res.data_ptr(),
             None if normed is None else normed.data_ptr(), x_q.data_ptr(), a_s.data_ptr(), M, K,
             _DTYPE_IDS[x.dtype], _stream_ptr(x.device))
-    _lib.check(rc, "b200q_add_rmsnorm_quant_i8", f"M={M} K={K}")
+    if rc:
+        _lib.check(rc, "b200q_add_rmsnorm_quant_i8", f"M={M} K={K}")
     return (x_q, a_s, None if new_res is None else new_res.view(x.shape),
             None if normed is None else normed.view(x.shape))
 
@@ -168,11 +199,12 @@ def silu_mul_quantize_int8(gate_up: torch.Tensor, return_act: bool = False):
     x_q = torch.empty((M, inter), dtype=torch.int8, device=gate_up.device)
     a_s = torch.empty((M,), dtype=torch.float32, device=gate_up.device)
     act = torch.empty((M, inter), dtype=gate_up.dtype, device=gate_up.device) if return_act else None
-    with torch.cuda.device(gate_up.device):
+    with _on_device(gate_up.device):
         rc = _lib.lib().b200q_silu_mul_quant_i8(g2.data_ptr(), two_i, None if act is None else act.data_ptr(),
                                                 x_q.data_ptr(), a_s.data_ptr(), M, inter,
                                                 _DTYPE_IDS[gate_up.dtype], _stream_ptr(gate_up.device))
-    _lib.check(rc, "b200q_silu_mul_quant_i8", f"M={M} I={inter}")
+    if rc:
+        _lib.check(rc, "b200q_silu_mul_quant_i8", f"M={M} I={inter}")
     return x_q, a_s, None if act is None else act.view(*gate_up.shape[:-1], inter)
 
 
@@ -214,14 +246,15 @@ def apply_int8_weight_only_linear(
     M = x_2d.shape[0]
     y = torch.empty((M, N), dtype=x.dtype, device=x.device)
     L = _lib.lib()
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         ws_bytes = L.b200q_workspace_bytes(_lib.OP_W8A16, M, N, K)
         ws = _workspace(x.device, ws_bytes)
         rc = L.b200q_w8a16_gemm(x_2d.data_ptr(), qweight.data_ptr(), scales.data_ptr(),
                                 None if bias is None else bias.data_ptr(), y.data_ptr(), M, N, K,
                                 _DTYPE_IDS[x.dtype], None if ws is None else ws.data_ptr(),
                                 0 if ws is None else ws.numel(), _stream_ptr(x.device))
-    _lib.check(rc, "b200q_w8a16_gemm", f"M={M} N={N} K={K}")
+    if rc:
+        _lib.check(rc, "b200q_w8a16_gemm", f"M={M} N={N} K={K}")
     return y.view(*x.shape[:-1], N)
 
 
@@ -276,7 +309,7 @@ def apply_w8a8_linear(
             raise RuntimeError(f"out must be a contiguous [{M}, {N}] {out_dtype} tensor on {x_q.device}")
         y = out
     L = _lib.lib()
-    with torch.cuda.device(x_q.device):
+    with _on_device(x_q.device):
         ws_bytes = L.b200q_workspace_bytes(_lib.OP_W8A8, M, N, K)
         ws = _workspace(x_q.device, ws_bytes)
         rc = L.b200q_w8a8_gemm(x_q.data_ptr(), a_scales.data_ptr(), qweight.data_ptr(),
@@ -284,7 +317,8 @@ def apply_w8a8_linear(
                                y.data_ptr(), M, N, K, _DTYPE_IDS[out_dtype],
                                None if ws is None else ws.data_ptr(),
                                0 if ws is None else ws.numel(), _stream_ptr(x_q.device))
-    _lib.check(rc, "b200q_w8a8_gemm", f"M={M} N={N} K={K}")
+    if rc:
+        _lib.check(rc, "b200q_w8a8_gemm", f"M={M} N={N} K={K}")
     return y if out_shape is None else y.view(out_shape)
 
 
@@ -301,11 +335,12 @@ def w8a8_int32_accumulators(x_q: torch.Tensor, qweight: torch.Tensor) -> torch.T
     N = qweight.shape[0]
     acc = torch.empty((M, N), dtype=torch.int32, device=x_q.device)
     L = _lib.lib()
-    with torch.cuda.device(x_q.device):
+    with _on_device(x_q.device):
         ws_bytes = L.b200q_workspace_bytes(_lib.OP_W8A8, M, N, K)
         ws = _workspace(x_q.device, ws_bytes)
         rc = L.b200q_w8a8_gemm_i32(x_q.data_ptr(), qweight.data_ptr(), acc.data_ptr(), M, N, K,
                                    None if ws is None else ws.data_ptr(),
                                    0 if ws is None else ws.numel(), _stream_ptr(x_q.device))
-    _lib.check(rc, "b200q_w8a8_gemm_i32", f"M={M} N={N} K={K}")
+    if rc:
+        _lib.check(rc, "b200q_w8a8_gemm_i32", f"M={M} N={N} K={K}")
     return acc
