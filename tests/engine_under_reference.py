@@ -152,7 +152,22 @@ def _runner_entry(config, rank, event):
     import os
     _install(os.environ["ENGINE_HARNESS_IMPL"], os.environ["ENGINE_HARNESS_QUANTIZED"] == "1")
     from nanovllm.engine.model_runner import ModelRunner
-    return ModelRunner(config, rank, event)
+    if os.environ.get("ENGINE_HARNESS_PEER") != "1":
+        return ModelRunner(config, rank, event)
+
+    class PeerRunner(ModelRunner):
+        """Installs this package's peer-memory communicator (fused decode GEMM + all-reduce,
+        one-trip / two-shot all-reduce kernels) once the process group exists and before the
+        first forward pass; everything else is the reference's runner."""
+
+        def warmup_model(self):
+            from tiny_vllm_b200.layers import linear as our_linear
+            from tiny_vllm_b200.layers.tp_comm import PeerAllReduce
+            hidden = self.config.hf_config.hidden_size
+            our_linear.set_tp_all_reduce(PeerAllReduce(max_bytes=self.config.max_num_batched_tokens * hidden * 2))
+            super().warmup_model()
+
+    return PeerRunner(config, rank, event)
 
 
 def run(args) -> None:
@@ -165,6 +180,7 @@ def run(args) -> None:
     ours = args.impl == "ours"
     os.environ["ENGINE_HARNESS_IMPL"] = args.impl          # read by the spawned workers
     os.environ["ENGINE_HARNESS_QUANTIZED"] = "1" if args.mode != "bf16" else "0"
+    os.environ["ENGINE_HARNESS_PEER"] = "1" if (args.peer and ours and args.tp > 1) else "0"
     _install(args.impl, args.mode != "bf16")
     if ours:
         from tiny_vllm_b200 import _lib
@@ -206,7 +222,8 @@ def run(args) -> None:
     outputs, stats = llm.generate_with_stats(prompts(args.seqs), sp)
     torch.cuda.synchronize()
     ok = len(outputs) == args.seqs and all(len(o["token_ids"]) == args.out for o in outputs)
-    line = {"impl": args.impl, "mode": args.mode, "tp": args.tp, "ok": ok, "linear_module": linear_module,
+    line = {"impl": args.impl, "mode": args.mode, "tp": args.tp, "peer_allreduce": bool(args.peer and ours and args.tp > 1),
+            "ok": ok, "linear_module": linear_module,
             "graphs": 0 if args.eager else len(getattr(llm.model_runner, "graphs", {})),
             "graph_batch_sizes": None if args.eager else sorted(getattr(llm.model_runner, "graph_bs", [])),
             "init_seconds": round(init_s, 1), "seqs": args.seqs, "in": [args.in_min, args.in_max], "out": args.out,
@@ -246,6 +263,8 @@ def main() -> None:
     r.add_argument("--max-num-seqs", type=int, default=512)
     r.add_argument("--max-num-batched-tokens", type=int, default=16384)
     r.add_argument("--eager", action="store_true")
+    r.add_argument("--peer", action="store_true",
+                   help="with --impl ours --tp N: this package's peer-memory all-reduce instead of NCCL")
     r.add_argument("--tp", type=int, default=1, help="tensor-parallel ranks (the engine spawns tp - 1 workers)")
     args = ap.parse_args()
     make(args) if args.cmd == "make" else run(args)
